@@ -9,15 +9,18 @@ are valid in every layer cache of the group.  A layer cache is two tensors
 ``page * block_size + offset`` holds one token (the reference keeps
 ``[layers * blocks, block_size, kv_dim]`` and offsets the block id by the
 layer, src/alofa/engine/executor.mojo:117-127, 301-310).  Slot-state caches
-are one tensor ``[max_requests, *shape]`` each."""
+are one tensor ``[max_requests, *shape]`` each.  A cache of one row per token
+(:class:`~alofa_b200.parts.base.PagedRows`) is one tensor
+``[num_pages * block_size, width]`` in a group like any other."""
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
 from ..errors import AlofaError
-from ..parts.base import PagedKV, SlotState
+from ..parts.base import PagedKV, PagedRows, SlotState
 
 
 @dataclass
@@ -26,7 +29,7 @@ class LayerCache:
 
     group: int
     k: torch.Tensor
-    v: torch.Tensor
+    v: Optional[torch.Tensor] = None  # None: a cache of one row per token (PagedRows), held in ``k``
 
 
 @dataclass
@@ -40,7 +43,7 @@ def group_windows(plan: dict) -> list:
     """The distinct windows of a cache plan, all-keys (None) first; empty when
     no layer wants pages (the model then has state slots only, and neither the
     cache manager nor the scheduler books a page for it)."""
-    windows = {spec.window for spec in plan.values() if isinstance(spec, PagedKV)}
+    windows = {spec.window for spec in plan.values() if isinstance(spec, (PagedKV, PagedRows))}
     return ([None] if None in windows else []) + sorted(w for w in windows if w is not None)
 
 
@@ -63,6 +66,14 @@ class CacheStorage:
                 v = torch.zeros(shape, dtype=dtype, device=device)
                 self.caches[idx] = LayerCache(gi, k, v)
                 self.bytes += 2 * k.numel() * k.element_size()
+            elif isinstance(spec, PagedRows):
+                if spec.window not in windows:
+                    raise AlofaError("invalid_argument", "no cache group for this window", f"window={spec.window} groups={windows}")
+                gi = windows.index(spec.window)
+                g = groups[gi]
+                rows = torch.zeros((g.num_pages * g.block_size, spec.width), dtype=dtype, device=device)
+                self.caches[idx] = LayerCache(gi, rows, None)
+                self.bytes += rows.numel() * rows.element_size()
             elif isinstance(spec, SlotState):
                 st = torch.zeros((max_requests,) + tuple(spec.shape), dtype=spec.dtype, device=device)
                 self.caches[idx] = StateCache(st)
@@ -84,4 +95,6 @@ class CacheStorage:
         for spec in plan.values():
             if isinstance(spec, PagedKV):
                 out[spec.window] = out.get(spec.window, 0) + 2 * spec.num_kv_heads * spec.head_dim * width
+            elif isinstance(spec, PagedRows):
+                out[spec.window] = out.get(spec.window, 0) + spec.width * width
         return out

@@ -73,9 +73,13 @@ def _ensure_builtin() -> None:
 
 
 def architecture_name_of(obj: dict, origin: str) -> str:
+    """``architectures: [name, ...]`` (the first counts) or ``architecture: name``."""
+    single = obj.get("architecture")
+    if "architectures" not in obj and isinstance(single, str) and single:
+        return single
     names = obj.get("architectures")
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise AlofaError("parse", "config.json must name its architecture in 'architectures'", f"config={origin}")
+        raise AlofaError("parse", "config.json must name its architecture in 'architectures' or 'architecture'", f"config={origin}")
     return names[0]
 
 

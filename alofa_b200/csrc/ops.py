@@ -527,3 +527,190 @@ def splitk_reduce(out, partial, bias, splits: int, epi: int) -> None:
         ),
         "splitk_reduce",
     )
+
+
+# -- latent attention, sandwich norms, routed feed-forwards -------------------------------------------
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "relu": 4}
+_L = ctypes.c_longlong
+
+
+def _latent():
+    lib = _libs.get("latent")
+    if lib is None:
+        lib = load_library("alofa_latent", ["kernels/latent.cu"])
+        sigs = {
+            "alofa_latent_prepare": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+            "alofa_latent_query_turn": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_rotary_interleaved": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_gemm_batched": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _P],
+            "alofa_activate": [_P, _P, _P, _L, _I, _I, _I, _P],
+            "alofa_latent_attention": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+            "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
+            "alofa_concat_rows": [_P, _P, _P, _I, _I, _I, _P],
+            "alofa_moe_route": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_moe_sort": [_P, _P, _P, _I, _I, _I, _I, _P],
+            "alofa_moe_scatter": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
+            "alofa_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["latent"] = lib
+    return lib
+
+
+def latent_prepare(cq, cache_rows, lat, wq, wkv, freq, positions, slot_map, q_rank: int, kv_rank: int, rot: int, rot_dims: int, eps: float) -> None:
+    """From the stacked down-projection ``lat`` [T, q_rank + kv_rank + rot]
+    (fp32): ``cq`` = RMSNorm of the first part; the cache row of each token =
+    [RMSNorm of the second part | the third part, its first ``rot_dims``
+    numbers turned by the token's position].  ``cache_rows`` None: no write."""
+    f32 = torch.float32
+    n = lat.shape[0]
+    if lat.shape[1] != q_rank + kv_rank + rot or tuple(cq.shape) != (n, q_rank) or (cache_rows is not None and cache_rows.shape[1] != kv_rank + rot):
+        raise AlofaError("invalid_argument", "latent_prepare sizes disagree", f"lat={tuple(lat.shape)} cq={tuple(cq.shape)}")
+    _done(
+        _latent().alofa_latent_prepare(
+            _dev(cq, "cq"), _dev(cache_rows, "cache", cq.dtype) if cache_rows is not None else None, _dev(lat, "lat", f32), _dev(wq, "wq", f32),
+            _dev(wkv, "wkv", f32), _dev(freq, "freq", f32) if rot_dims else None, _dev(positions, "positions", torch.int32),
+            _dev(slot_map, "slot_map", torch.int32) if cache_rows is not None else None, n, q_rank, kv_rank, rot, rot_dims, float(eps), _is_bf16(cq, "cq"), _stream(),
+        ),
+        "latent_prepare",
+    )
+
+
+def latent_query_turn(qa, q, freq, positions, heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int) -> None:
+    """The rotated part of q [T, heads * (dim + rot)] turned by position into
+    columns ``kv_rank``.. of qa [T, heads * (kv_rank + rot)]."""
+    n = q.shape[0]
+    if q.shape[1] != heads * (dim + rot) or tuple(qa.shape) != (n, heads * (kv_rank + rot)):
+        raise AlofaError("invalid_argument", "latent_query_turn sizes disagree", f"q={tuple(q.shape)} qa={tuple(qa.shape)}")
+    if rot == 0:
+        return
+    _done(
+        _latent().alofa_latent_query_turn(_dev(qa, "qa", q.dtype), _dev(q, "q"), _dev(freq, "freq", torch.float32) if rot_dims else None,
+                                          _dev(positions, "positions", torch.int32), n, heads, dim, rot, rot_dims, kv_rank, _is_bf16(q, "q"), _stream()),
+        "latent_query_turn",
+    )
+
+
+def rotary_interleaved(x, freq, positions, heads: int, hd: int, rot_dims: int) -> None:
+    """Turn the pairs (2i, 2i+1), i < rot_dims / 2, of every head of the view
+    ``x`` [T, heads, hd] (unit stride inside a row) in place."""
+    if x.shape[0] == 0 or heads == 0 or rot_dims == 0:
+        return
+    if not x.is_cuda or x.stride(2) != 1 or x.stride(1) != hd:
+        raise AlofaError("invalid_argument", "rotary_interleaved wants heads packed in rows", f"strides={x.stride()}")
+    _done(
+        _latent().alofa_rotary_interleaved(x.data_ptr(), _dev(freq, "freq", torch.float32), _dev(positions, "positions", torch.int32), x.shape[0], heads, hd,
+                                           x.stride(0), rot_dims, _is_bf16(x, "x"), _stream()),
+        "rotary_interleaved",
+    )
+
+
+def gemm_batched(out, x, w, batches: int, m: int, n: int, k: int, ldx: int, x_batch: int, ldw: int, w_batch: int, ldo: int, out_batch: int,
+                 bias=None, bias_batch: int = 0, act: str = "none", tile_batch=None) -> None:
+    """``out_b[m, n] = act(x_b[m, :] . w_b[n, :] + bias_b[n])`` for every batch
+    b, operands addressed by row and batch strides (in elements) from the
+    tensors' first elements.  With ``tile_batch`` (int32, one entry per 64-row
+    tile) there is one x and one out and tile i uses the weight of batch
+    ``tile_batch[i]``; negative entries are skipped."""
+    for t, name in ((out, "out"), (x, "x"), (w, "w")):
+        if not t.is_cuda:
+            raise AlofaError("unsupported", "kernels run on CUDA tensors only", f"{name} is on {t.device}")
+    _done(
+        _latent().alofa_gemm_batched(
+            out.data_ptr(), x.data_ptr(), w.data_ptr(), _dev(bias, "bias", torch.float32) if bias is not None else None,
+            _dev(tile_batch, "tile_batch", torch.int32) if tile_batch is not None else None, batches, m, n, k, ldx, x_batch, ldw, w_batch, ldo, out_batch,
+            bias_batch, ACTIVATIONS[act], _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
+        ),
+        "gemm_batched", f"batches={batches} M={m} N={n} K={k}",
+    )
+
+
+def activate(out, x, bias, act: str) -> None:
+    """out = act(x + bias): x fp32 [rows, n], out in its own dtype."""
+    rows, n = x.shape
+    _done(_latent().alofa_activate(_dev(out, "out"), _dev(x, "x", torch.float32), _dev(bias, "bias", torch.float32) if bias is not None else None,
+                                   rows, n, ACTIVATIONS[act], _is_bf16(out, "out"), _stream()), "activate")
+
+
+def latent_attention(out, qa, cache_rows, sink, positions, seq_of_token, block_table, page_size: int, heads: int, kv_rank: int, rot: int, window, scale: float) -> None:
+    """Causal attention of absorbed queries qa [T, heads * (kv_rank + rot)]
+    over the paged rows [c | kr]; out [T, heads * kv_rank] = sum_j p_j c_j,
+    softmax in fp32 with ``exp(sink[h])`` (fp32 [heads], or None) as one more
+    term of the denominator."""
+    n = qa.shape[0]
+    if qa.shape[1] != heads * (kv_rank + rot) or tuple(out.shape) != (n, heads * kv_rank) or cache_rows.shape[1] != kv_rank + rot:
+        raise AlofaError("invalid_argument", "latent_attention sizes disagree", f"qa={tuple(qa.shape)} out={tuple(out.shape)} cache={tuple(cache_rows.shape)}")
+    dt = qa.dtype
+    _done(
+        _latent().alofa_latent_attention(
+            _dev(out, "out", dt), _dev(qa, "qa"), _dev(cache_rows, "cache", dt), _dev(sink, "sink", torch.float32) if sink is not None else None,
+            _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+            block_table.shape[1], page_size, n, heads, kv_rank, rot, int(window or 0), float(scale), _is_bf16(qa, "qa"), _stream(),
+        ),
+        "latent_attention", f"heads={heads} kv_rank={kv_rank} rot={rot}",
+    )
+
+
+def sandwich_norm(h, y, w_post, eps_post: float, x=None, w_next=None, eps_next: float = 0.0) -> None:
+    """``h += rmsnorm(y) * w_post`` (fp32 stream); with ``x`` also ``x =
+    rmsnorm(h) * w_next`` of the updated rows, in x's dtype."""
+    rows, hidden = h.shape
+    if tuple(y.shape) != (rows, hidden) or (x is not None and tuple(x.shape) != (rows, hidden)):
+        raise AlofaError("invalid_argument", "sandwich_norm sizes disagree", f"h={tuple(h.shape)} y={tuple(y.shape)}")
+    f32 = torch.float32
+    _done(
+        _latent().alofa_sandwich_norm(_dev(h, "h", f32), _dev(y, "y", f32), _dev(w_post, "w_post", f32), float(eps_post), _dev(x, "x") if x is not None else None,
+                                      _dev(w_next, "w_next", f32) if x is not None else None, float(eps_next), rows, hidden, _is_bf16(x, "x") if x is not None else 0, _stream()),
+        "sandwich_norm",
+    )
+
+
+def concat_rows(out, a, b) -> None:
+    """out [T, 2 * hidden] = [a | b] from two fp32 matrices, in out's dtype."""
+    rows, hidden = a.shape
+    if tuple(b.shape) != (rows, hidden) or tuple(out.shape) != (rows, 2 * hidden):
+        raise AlofaError("invalid_argument", "concat_rows sizes disagree", f"a={tuple(a.shape)} b={tuple(b.shape)} out={tuple(out.shape)}")
+    _done(_latent().alofa_concat_rows(_dev(out, "out"), _dev(a, "a", torch.float32), _dev(b, "b", torch.float32), rows, hidden, _is_bf16(out, "out"), _stream()), "concat_rows")
+
+
+MOE_TILE = 64  # rows per tile of the sorted matrix: every expert's rows are padded to whole tiles
+
+
+def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = False, renormalize: bool = False) -> None:
+    """From router logits z [T, experts (+1)] fp32: the ``top`` experts of each
+    token by score (sigmoid, or softmax over the experts), their scores as
+    weights, and ``gate`` = sigmoid of the last column when given."""
+    i32, f32 = torch.int32, torch.float32
+    _done(
+        _latent().alofa_moe_route(_dev(choice, "choice", i32), _dev(weight, "weight", f32), _dev(gate, "gate", f32) if gate is not None else None, _dev(z, "z", f32),
+                                  z.shape[0], experts, top, z.shape[1], 1 if softmax else 0, 1 if renormalize else 0, _stream()),
+        "moe_route", f"experts={experts} top={top}",
+    )
+
+
+def moe_sort(dest, tile_expert, choice, experts: int, tile: int = MOE_TILE) -> None:
+    """Rows of the (token, choice) pairs in a matrix sorted by expert, every
+    expert padded to whole tiles: ``dest`` [pairs], ``tile_expert`` [tiles]."""
+    i32 = torch.int32
+    _done(_latent().alofa_moe_sort(_dev(dest, "dest", i32), _dev(tile_expert, "tile_expert", i32), _dev(choice, "choice", i32), choice.numel(), experts, tile,
+                                   tile_expert.numel(), _stream()), "moe_sort")
+
+
+def moe_scatter(xs, x, weight, dest, top: int) -> None:
+    """xs[dest[t, k]] = x[t] (times weight[t, k] when given)."""
+    _done(_latent().alofa_moe_scatter(_dev(xs, "xs", x.dtype), _dev(x, "x"), _dev(weight, "weight", torch.float32) if weight is not None else None,
+                                      _dev(dest, "dest", torch.int32), dest.numel(), top, x.shape[1], _is_bf16(x, "x"), _stream()), "moe_scatter")
+
+
+def moe_combine(y, ys, dest, weight, shared, gate, top: int) -> None:
+    """y[t] = sum_k (weight[t, k] *) ys[dest[t, k]] + (gate[t] *) shared[t], fp32."""
+    f32 = torch.float32
+    _done(
+        _latent().alofa_moe_combine(_dev(y, "y", f32), _dev(ys, "ys", f32), _dev(dest, "dest", torch.int32), _dev(weight, "weight", f32) if weight is not None else None,
+                                    _dev(shared, "shared", f32) if shared is not None else None, _dev(gate, "gate", f32) if gate is not None else None,
+                                    y.shape[0], top, y.shape[1], _stream()),
+        "moe_combine",
+    )

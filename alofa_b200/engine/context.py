@@ -117,6 +117,7 @@ class StepContext:
         self.capturing = False  # the step is being recorded as a CUDA graph: launch shapes must not depend on this step's lengths
 
         self.any_hot = True  # some wanted row samples with a positive temperature
+        self.embedding_output = None  # fp32 [tokens, hidden]: kept by the model when a block asks for it
         self.pending = None  # a Pending: what the residual stream's own tensor still lacks
         # Small decode steps keep the stream as base + fixed-point accumulator (see open_stream)
         self.stream_acc = None  # int64 [2, rows, hidden], given by the step runner; both zero between steps

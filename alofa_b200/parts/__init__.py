@@ -1,6 +1,7 @@
 """The parts models are put together from, and their registries."""
 from .base import (  # noqa: F401
     PagedKV,
+    PagedRows,
     Part,
     Runtime,
     SlotState,
@@ -8,5 +9,5 @@ from .base import (  # noqa: F401
     build_part,
     register_part,
 )
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401,E402
+from . import attention, block, embedding, feed_forward, latent_attention, norm, position, routed  # noqa: F401,E402
 from .model import Model, expected_tensors  # noqa: F401,E402

@@ -14,7 +14,7 @@ Interfaces (``ctx`` is the step's :class:`~alofa_b200.engine.context.StepContext
 * norm: ``forward(ctx, h, rows=None) -> x`` in the compute dtype;
 * position: ``rotary_table()`` (cos/sin table and rotary_dim, or None) and
   ``apply(ctx, q, k)`` for encodings that are not rotary;
-* mixer: ``cache_spec()`` (PagedKV, SlotState or None) and
+* mixer: ``cache_spec()`` (PagedKV, PagedRows, SlotState or None) and
   ``forward(ctx, x, h, cache, writes)`` which adds its output into ``h``;
 * feed_forward: ``forward(ctx, x, h)`` which adds its output into ``h``;
 * block: ``cache_spec()`` and ``forward(ctx, h, cache, writes)``;
@@ -51,6 +51,16 @@ class PagedKV:
 
     num_kv_heads: int
     head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class PagedRows:
+    """A mixer's need of a paged cache that keeps ONE row of ``width`` numbers
+    per token (a latent that keys and values are both made from), in the
+    compute dtype: ``window`` None = all rows."""
+
+    width: int
     window: Optional[int] = None
 
 

@@ -24,13 +24,14 @@ class TokenEmbedding(Part):
         super().__init__(spec, rt)
         self.vocab = int(self.param("vocab_size"))
         self.hidden = int(self.param("hidden_size"))
+        self.name = self.prefix + str(self.params.get("weight_name", "weight"))
         self.weight = None
 
     def tensors(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.hidden))}
+        return {self.name: TensorSpec((self.vocab, self.hidden))}
 
     def load(self, state):
-        self.weight = state[self.prefix + "weight"]
+        self.weight = state[self.name]
 
     def forward(self, ctx, h):
         ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
@@ -44,13 +45,14 @@ class LinearHead(Part):
         self.vocab = int(self.param("vocab_size"))
         self.hidden = int(self.param("hidden_size"))
         self.tied_to = self.params.get("tied_to")
+        self.name = self.prefix + str(self.params.get("weight_name", "weight"))
         self.linear = None
 
     def tensors(self):
-        return {self.prefix + "weight": TensorSpec((self.vocab, self.hidden), optional=self.tied_to is not None)}
+        return {self.name: TensorSpec((self.vocab, self.hidden), optional=self.tied_to is not None)}
 
     def load(self, state):
-        name = self.prefix + "weight"
+        name = self.name
         if name in state:
             weight = state[name]
         elif self.tied_to is not None and self.tied_to in state:

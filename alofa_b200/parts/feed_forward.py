@@ -7,9 +7,10 @@ from __future__ import annotations
 
 import torch
 
+from ..csrc import ops
 from ..errors import AlofaError
-from .base import Part, TensorSpec, register_part
-from .linear import GATED, RESIDUAL, Linear, add_into_stream
+from .base import Part, TensorSpec, as_float32_vector, register_part
+from .linear import GATED, RESIDUAL, STORE, Linear, add_into_stream
 
 
 class GatedMLP(Part):
@@ -49,4 +50,56 @@ class GatedMLP(Part):
         add_into_stream(ctx, self.down, h, act)
 
 
+class DenseMLP(Part):
+    """``Wdown act(Wup x (+ bup)) (+ bdown)`` with tensors ``<prefix>up``,
+    ``<prefix>down`` (``.b`` for the biases); ``activation``: gelu_erf (the
+    exact one), gelu_tanh, silu, relu.  The activation is taken on the fp32
+    sums, before they are rounded to the compute dtype."""
+
+    family = "feed_forward"
+    graph_safe = True
+    stores_output = True  # forward(..., store=True) writes its output instead of adding it
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.act = str(self.param("activation", "gelu_erf"))
+        self.bias = bool(self.params.get("bias", False))
+        if self.act not in ops.ACTIVATIONS:
+            raise AlofaError("unsupported", "unknown activation", f"activation={self.act} known={sorted(ops.ACTIVATIONS)}")
+        self.up = self.down = None
+
+    def tensors(self):
+        pre = self.prefix
+        t = {pre + "up": TensorSpec((self.inter, self.hidden)), pre + "down": TensorSpec((self.hidden, self.inter))}
+        if self.bias:
+            t[pre + "up.b"] = TensorSpec((self.inter,))
+            t[pre + "down.b"] = TensorSpec((self.hidden,))
+        return t
+
+    def load(self, state):
+        pre = self.prefix
+        self.up_bias = as_float32_vector(state[pre + "up.b"]) if self.bias else None
+        self.up = Linear(state[pre + "up"], None, STORE)
+        self.down = Linear(state[pre + "down"], as_float32_vector(state[pre + "down.b"]) if self.bias else None, STORE)
+
+    def scratch_row_bytes(self) -> int:
+        return 8 * self.inter + 4 * self.hidden
+
+    def forward(self, ctx, x, h, store=False):
+        n = x.shape[0]
+        sums = ctx.buf((n, self.inter), torch.float32)
+        self.up(sums, x, buf=ctx.buf)
+        mid = ctx.buf((n, self.inter), self.rt.dtype)
+        ops.activate(mid, sums, self.up_bias, self.act)
+        if store:
+            self.down(h, mid, buf=ctx.buf)
+        else:
+            y = ctx.buf((n, self.hidden), torch.float32)
+            self.down(y, mid, buf=ctx.buf)
+            h.add_(y)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "mlp", DenseMLP)

@@ -23,6 +23,8 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.run = [(e.layer, i if e.cache is None else e.cache) for i, e in enumerate(spec.run)]
+        # a block may read the embedding output of the step's tokens later on (ctx.embedding_output)
+        self.keeps_embedding = any(getattr(block, "needs_embedding_output", False) for block in self.layers)
 
     def parts(self):
         return [self.embedding, *self.layers, self.final_norm, self.head]
@@ -47,7 +49,7 @@ class Model:
         layer that needs most): what the step runner sizes its arena from."""
         hidden = self.spec.hidden_size
         per_layer = max([getattr(block, "scratch_row_bytes", lambda: 0)() for block in self.layers] + [8 * hidden])
-        return 4 * hidden + 4 * hidden, per_layer
+        return 4 * hidden + 4 * hidden + (4 * hidden if self.keeps_embedding else 0), per_layer
 
     def cache_plan(self) -> dict:
         """run index -> cache spec, for the entries that own a cache."""
@@ -59,6 +61,9 @@ class Model:
         h = ctx.buf((ctx.n_tokens, self.spec.hidden_size), torch.float32)
         ctx.open_stream(h)
         self.embedding.forward(ctx, h)
+        if self.keeps_embedding:
+            ctx.embedding_output = ctx.buf(tuple(h.shape), torch.float32)
+            ctx.embedding_output.copy_(h)
         for i, (layer, cache) in enumerate(self.run):
             block = self.layers[layer]
             if not getattr(block, "absorbs_pending", False):

@@ -18,13 +18,14 @@ class RMSNorm(Part):
         super().__init__(spec, rt)
         self.size = int(self.param("size"))
         self.eps = float(self.param("eps"))
+        self.name = self.prefix + str(self.params.get("weight_name", "weight"))  # the tensor's name: prefix + "weight" unless the spec says otherwise
         self.weight = None
 
     def tensors(self):
-        return {self.prefix + "weight": TensorSpec((self.size,), "ones")}
+        return {self.name: TensorSpec((self.size,), "ones")}
 
     def load(self, state):
-        self.weight = as_float32_vector(state[self.prefix + "weight"])
+        self.weight = as_float32_vector(state[self.name])
 
     absorbs_pending = True  # adds split-K partial sums owed to h while reading it
     gives_normed_rows = True  # forward(lazy=True) may hand its reader rows still to be made

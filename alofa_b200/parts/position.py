@@ -55,6 +55,51 @@ class RotaryNeox(Part):
         return self._table, self.rotary_dim
 
 
+class RotaryInterleaved(Part):
+    """Rotary encoding on neighbouring pairs: dimension 2i goes with 2i + 1, i
+    < dims / 2; at position p the pair (u, v) becomes (u cos a - v sin a, v cos
+    a + u sin a) with a = p * f_i, f_i = base^(-2i / dims).  f_i is rounded to
+    fp32 once (from the power in f64); position, angle, cosine and sine are
+    fp32 in the kernels that turn, so no table and no longest position."""
+
+    family = "position"
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.dims = int(self.param("dims"))
+        self.base = float(self.param("base"))
+        if self.dims < 0 or self.dims % 2 or self.base <= 0:
+            raise AlofaError("unsupported", "rotary dims must be even and the base positive", f"dims={self.dims} base={self.base}")
+        self._freq = None
+
+    def key(self):
+        return ("rotary_interleaved", self.dims, self.base)
+
+    def load(self, state):
+        tables = state.setdefault("__rotary_tables__", {})
+        if self.key() not in tables:
+            i = np.arange(max(self.dims // 2, 1), dtype=np.float64)
+            freq = np.power(np.float64(self.base), -2.0 * i / max(self.dims, 1)).astype(np.float32)
+            tables[self.key()] = torch.from_numpy(freq).to(self.rt.device)
+        self._freq = tables[self.key()]
+
+    def frequencies(self) -> torch.Tensor:
+        """f_i as fp32 [dims / 2] on the device."""
+        return self._freq
+
+    def rotary_table(self):
+        return None, 0  # no table: mixers that hold whole heads call apply()
+
+    def apply(self, ctx, q, k):
+        """Turn q [T, heads, hd] and k [T, kv_heads, hd] (views) in place."""
+        from ..csrc import ops
+
+        ops.rotary_interleaved(q, self._freq, ctx.positions, q.shape[1], q.shape[2], self.dims)
+        if k.shape[1]:
+            ops.rotary_interleaved(k, self._freq, ctx.positions, k.shape[1], k.shape[2], self.dims)
+
+
 class NoPosition(Part):
     """No position encoding: queries and keys are used as projected."""
 
@@ -66,4 +111,5 @@ class NoPosition(Part):
 
 
 register_part("position", "rotary_neox", RotaryNeox)
+register_part("position", "rotary_interleaved", RotaryInterleaved)
 register_part("position", "none", NoPosition)

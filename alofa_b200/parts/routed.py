@@ -1,0 +1,111 @@
+"""Routed feed-forward (mixture of experts).
+
+``experts`` small feed-forwards ``Wdown act(Wup .)`` without biases, of which
+every token uses ``top``.  Router logits ``z = x Wr^T`` and the scores made from
+them are fp32 (``score``: "sigmoid" per expert, or "softmax" over the experts);
+the ``top`` largest scores choose the experts and are their weights
+(``renormalize``: divided by their sum).  The weight multiplies the expert's
+input (``weight_on_input``) or its output.  A shared expert of the same form
+(``shared_ff`` > 0) runs for every token and is added, times ``sigmoid(x
+wsg^T)`` when ``shared_gate`` is set.
+
+Nothing here asks the host: the tokens' choices stay on the device.  The
+(token, choice) pairs are sorted by expert into a matrix in which every expert's
+rows are padded to whole tiles, so one launch per projection multiplies each
+tile by its expert's weights; the outputs are gathered back and added in the
+order of the choices."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..errors import AlofaError
+from .base import Part, TensorSpec, register_part
+from .feed_forward import DenseMLP
+from .linear import STORE, Linear
+
+
+class RoutedExperts(Part):
+    family = "feed_forward"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.experts = int(p("experts"))
+        self.top = int(p("top"))
+        self.ff = int(p("expert_ff"))
+        self.shared_ff = int(self.params.get("shared_ff") or 0)
+        self.act = str(p("activation", "gelu_erf"))
+        self.score = str(p("score", "sigmoid"))
+        self.renormalize = bool(self.params.get("renormalize", False))
+        self.weight_on_input = bool(self.params.get("weight_on_input", False))
+        self.shared_gate = bool(self.params.get("shared_gate", False)) and self.shared_ff > 0
+        if self.act not in ops.ACTIVATIONS or self.score not in ("sigmoid", "softmax"):
+            raise AlofaError("unsupported", "unknown activation or score of a routed feed-forward", f"activation={self.act} score={self.score}")
+        if not 0 < self.top <= min(self.experts, 32):
+            raise AlofaError("invalid_argument", "top must lie in [1, min(experts, 32)]", f"top={self.top} experts={self.experts}")
+        self.shared = None
+        if self.shared_ff:
+            from ..config.spec import PartSpec
+
+            self.shared = DenseMLP(PartSpec("mlp", {"hidden_size": self.hidden, "intermediate_size": self.shared_ff, "activation": self.act, "bias": False},
+                                            prefix=self.prefix + "shared."), rt)
+
+    def tensors(self):
+        pre = self.prefix
+        t = {pre + "router": TensorSpec((self.experts, self.hidden))}
+        for e in range(self.experts):
+            t[pre + f"e{e}.up"] = TensorSpec((self.ff, self.hidden))
+            t[pre + f"e{e}.down"] = TensorSpec((self.hidden, self.ff))
+        if self.shared is not None:
+            t.update(self.shared.tensors())
+            if self.shared_gate:
+                t[pre + "shared.sg"] = TensorSpec((1, self.hidden))
+        return t
+
+    def load(self, state):
+        pre = self.prefix
+        rows = [state[pre + "router"]] + ([state[pre + "shared.sg"]] if self.shared_gate else [])
+        self.router = torch.cat(rows, dim=0).to(torch.float32).contiguous()  # the router is fp32 whatever the compute dtype
+        self.up = torch.stack([state[pre + f"e{e}.up"] for e in range(self.experts)]).contiguous()  # [E, ff, hidden]
+        self.down = torch.stack([state[pre + f"e{e}.down"] for e in range(self.experts)]).contiguous()  # [E, hidden, ff]
+        if self.shared is not None:
+            self.shared.load(state)
+
+    def scratch_row_bytes(self) -> int:
+        return self.top * (4 * self.hidden + 4 * self.ff + 4 * self.hidden) + 8 * self.hidden + 4 * self.shared_ff + 4 * (self.experts + 1)
+
+    def forward(self, ctx, x, h, store=False):
+        n, dt, top, tile = x.shape[0], self.rt.dtype, self.top, ops.MOE_TILE
+        i32, f32 = torch.int32, torch.float32
+        z = ctx.buf((n, self.router.shape[0]), f32)
+        ops.gemm_generic(z, x, self.router, None, ops.EPI_STORE)
+        choice, weight = ctx.buf((n, top), i32), ctx.buf((n, top), f32)
+        gate = ctx.buf((n,), f32) if self.shared_gate else None
+        ops.moe_route(choice, weight, gate, z, self.experts, top, self.score == "softmax", self.renormalize)
+        pairs = n * top
+        tiles = -(-pairs // tile) + self.experts  # every expert may end on a tile that is not full
+        dest, tile_expert = ctx.buf((n, top), i32), ctx.buf((tiles,), i32)
+        ops.moe_sort(dest, tile_expert, choice, self.experts, tile)
+        rows = tiles * tile
+        xs = ctx.buf((rows, self.hidden), dt)
+        ops.moe_scatter(xs, x, weight if self.weight_on_input else None, dest, top)
+        mid = ctx.buf((rows, self.ff), dt)
+        ops.gemm_batched(mid, xs, self.up, 1, rows, self.ff, self.hidden, self.hidden, 0, self.hidden, self.ff * self.hidden, self.ff, 0,
+                         act=self.act, tile_batch=tile_expert)
+        ys = ctx.buf((rows, self.hidden), f32)
+        ops.gemm_batched(ys, mid, self.down, 1, rows, self.hidden, self.ff, self.ff, 0, self.ff, self.hidden * self.ff, self.hidden, 0, tile_batch=tile_expert)
+        shared = None
+        if self.shared is not None:
+            shared = ctx.buf((n, self.hidden), f32)
+            self.shared.forward(ctx, x, shared, store=True)
+        y = h if store else ctx.buf((n, self.hidden), f32)
+        ops.moe_combine(y, ys, dest, None if self.weight_on_input else weight, shared, gate, top)
+        if not store:
+            h.add_(y)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)
