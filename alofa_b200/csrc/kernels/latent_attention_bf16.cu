@@ -1,0 +1,256 @@
+// Latent attention on tensor cores for bfloat16, built per latent size
+// (-DKV_RANK=..., -DROT=...): prompt portions and decode tokens of a step.
+//
+// Every head of a token attends to the same cached rows [c | kr] (width D =
+// KV_RANK + ROT), so heads are packed on the row axis: row r of a request's
+// portion is (token r / heads, head r % heads), and a CTA owns 64 consecutive
+// rows, which lie contiguously in the absorbed-query matrix qa [T, heads, D].  A
+// decode token alone gives `heads` rows, a prompt portion many tiles.  Keys come
+// in blocks of 32 rows of the paged cache (cp.async, double buffered); the same
+// block in shared memory is the key operand (all D columns) and the value
+// operand (its first KV_RANK columns).  Eight warps: warp = (row group of 16
+// rows, half of the value columns).  Both halves of a row group compute the
+// group's scores S = Q K^T (mma.sync m16n8k16, fp32 sums over D), take the
+// streaming softmax in fp32 in registers (maximum, sum, exp2 of scores scaled by
+// scale * log2 e), round the weights to bfloat16 in the A-fragment layout, and
+// each adds P V for its half of the columns into fp32 accumulators in registers
+// (KV_RANK / 4 per thread).  The sink enters as the initial state of a row:
+// maximum = sink, sum = 1, nothing added to the output.
+//
+// Causal bound and window go by the row's own position; keys past the request's
+// length are never fetched (their rows in shared memory are zeroed).
+#include "common.cuh"
+
+#ifndef KV_RANK
+#define KV_RANK 64
+#endif
+#ifndef ROT
+#define ROT 16
+#endif
+
+namespace {
+
+constexpr int D = KV_RANK + ROT;
+constexpr int PITCH = D + 8;          // elements per row in shared memory: 16 bytes of padding keep ldmatrix off bank conflicts
+constexpr int BM = 64, BN = 32;
+constexpr int THREADS = 256;
+constexpr int HALF = KV_RANK / 2;     // value columns per warp
+constexpr int NT = HALF / 8;          // n-tiles of the output per warp
+static_assert(KV_RANK % 32 == 0 && D % 16 == 0, "latent sizes this kernel takes");
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src)); }
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa, const bf16* __restrict__ cache, const float* __restrict__ sink,
+                             const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_blocks,
+                             int page_size, int heads, int window, float scale_log2) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][PITCH]
+  bf16* Ks = Qs + BM * PITCH;                        // [2][BN][PITCH]
+  pdl_begin();
+  const int seq = blockIdx.y, tile = blockIdx.x;
+  const int t0 = q_start[seq], q_len = q_start[seq + 1] - t0;
+  const int rows = q_len * heads, r0 = tile * BM;
+  if (r0 >= rows) return;
+  const int n_keys = kv_len[seq];            // rows of this request in the cache after this step
+  const int pos0 = n_keys - q_len;           // position of the portion's first token
+  const int* table = block_table + (size_t)seq * max_blocks;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp & 3, ch = warp >> 2, g = lane >> 2, t = lane & 3;
+
+  // the query tile: 64 consecutive rows of qa
+  {
+    const bf16* src = qa + ((size_t)t0 * heads + r0) * D;
+    const int live = min(BM, rows - r0);
+    constexpr int CHUNKS = D / 8;
+    for (int e = tid; e < BM * CHUNKS; e += THREADS) {
+      const int r = e / CHUNKS, c = e - r * CHUNKS;
+      if (r < live) cp16(smem_addr(Qs + r * PITCH + c * 8), src + (size_t)r * D + c * 8);
+      else *reinterpret_cast<uint4*>(Qs + r * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  // keys this tile needs: up to the position of its last row, from the window's start of its first row
+  const int last_row = min(r0 + BM, rows) - 1;
+  const int key_hi = pos0 + last_row / heads;  // inclusive
+  int key_lo = 0;
+  if (window > 0) key_lo = max(0, pos0 + r0 / heads - window + 1);
+  const int b_lo = key_lo / BN, b_hi = key_hi / BN;
+
+  auto fetch = [&](int b, int buf) {
+    bf16* dst = Ks + (size_t)buf * BN * PITCH;
+    constexpr int CHUNKS = D / 8;
+    for (int e = tid; e < BN * CHUNKS; e += THREADS) {
+      const int j = e / CHUNKS, c = e - j * CHUNKS;
+      const int key = b * BN + j;
+      if (key <= key_hi) {
+        const int slot = table[key / page_size] * page_size + key % page_size;
+        cp16(smem_addr(dst + j * PITCH + c * 8), cache + (size_t)slot * D + c * 8);
+      } else {
+        *reinterpret_cast<uint4*>(dst + j * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  fetch(b_lo, 0);
+  cp_commit();
+
+  // this thread's two rows of its group: g and g + 8
+  int pos[2], first[2];
+  float m[2], l[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + rg * 16 + g + 8 * i;
+    const bool live = r < rows;
+    pos[i] = live ? pos0 + r / heads : -1;
+    first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
+    const bool sunk = live && sink != nullptr;
+    m[i] = sunk ? sink[r % heads] * 1.4426950408889634f : -INFINITY;
+    l[i] = sunk ? 1.f : 0.f;
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[j][k] = 0.f;
+
+  const uint32_t q_base = smem_addr(Qs + (rg * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8);
+  for (int b = b_lo; b <= b_hi; ++b) {
+    const int buf = (b - b_lo) & 1;
+    if (b < b_hi) fetch(b + 1, buf ^ 1);
+    cp_commit();
+    cp_wait<1>();
+    __syncthreads();
+    const bf16* Kb = Ks + (size_t)buf * BN * PITCH;
+    // S = Q K^T for 16 rows x 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s[j][k] = 0.f;
+    const uint32_t k_base = smem_addr(Kb + ((lane & 7) + (lane >> 4) * 8) * PITCH + ((lane >> 3) & 1) * 8);
+#pragma unroll 4
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      uint32_t a[4], b01[4], b23[4];
+      ldsm4(a, q_base + k0 * 2);
+      ldsm4(b01, k_base + k0 * 2);
+      ldsm4(b23, k_base + (16 * PITCH + k0) * 2);
+      mma16816(s[0], a, b01[0], b01[1]);
+      mma16816(s[1], a, b01[2], b01[3]);
+      mma16816(s[2], a, b23[0], b23[1]);
+      mma16816(s[3], a, b23[2], b23[3]);
+    }
+    // mask, streaming softmax (in units of log2)
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = k >> 1;
+        const int key = b * BN + j * 8 + 2 * t + (k & 1);
+        const float v = (key <= pos[i] && key >= first[i]) ? s[j][k] * scale_log2 : -INFINITY;
+        s[j][k] = v;
+        mx[i] = fmaxf(mx[i], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m[i], mx[i]);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      corr[i] = exp2f(m[i] - m_use);  // m = -inf: 0
+      m[i] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s[j][2 * i] = exp2f(s[j][2 * i] - m_use);
+        s[j][2 * i + 1] = exp2f(s[j][2 * i + 1] - m_use);
+        sum += s[j][2 * i] + s[j][2 * i + 1];
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[i] = l[i] * corr[i] + sum;
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      o[j][0] *= corr[0];
+      o[j][1] *= corr[0];
+      o[j][2] *= corr[1];
+      o[j][3] *= corr[1];
+    }
+    // O += P V over this warp's half of the value columns
+    const uint32_t v_base = smem_addr(Kb + ((lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + ch * HALF + (lane >> 4) * 8);
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      uint32_t p[4];
+      p[0] = pack2(s[2 * kk][0], s[2 * kk][1]);
+      p[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
+      p[2] = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      p[3] = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t v[4];
+        ldsm4_t(v, v_base + (kk * 16 * PITCH + j * 8) * 2);
+        mma16816(o[j], p, v[0], v[1]);
+        mma16816(o[j + 1], p, v[2], v[3]);
+      }
+    }
+    __syncthreads();  // the block is read out: its buffer may be refilled
+  }
+  cp_wait<0>();
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + rg * 16 + g + 8 * i;
+    if (r >= rows) continue;
+    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    bf16* dst = out + ((size_t)t0 * heads + r) * KV_RANK + ch * HALF + 2 * t;
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+      *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+  }
+}
+
+}  // namespace
+
+// qa [T, heads, D], out [T, heads, KV_RANK], cache [slots, D]: bfloat16.  max_q_len: the longest portion of the
+// step (or, for a recorded step, the longest it may hold).
+ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void* cache, const float* sink, const int* q_start, const int* kv_len,
+                                          const int* block_table, int max_blocks, int page_size, int n_seqs, int max_q_len, int heads, int window,
+                                          float scale, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return ALOFA_OK;
+  if (heads <= 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
+  const size_t smem = (size_t)(BM + 2 * BN) * PITCH * sizeof(bf16);
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(latent_attention_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    set = true;
+  }
+  const long long tiles = ((long long)max_q_len * heads + BM - 1) / BM;
+  if (tiles > 2147483647LL || n_seqs > 65535) return ALOFA_ERR_ARGUMENT;
+  launch_dep(latent_attention_bf16_kernel, dim3((unsigned)tiles, n_seqs), dim3(THREADS), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache, sink,
+             q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f);
+  return launch_status();
+}
+
+ALOFA_API int alofa_latent_attention_bf16_sizes(int* kv_rank, int* rot) {
+  *kv_rank = KV_RANK;
+  *rot = ROT;
+  return (int)((BM + 2 * BN) * PITCH * sizeof(bf16));
+}

@@ -12,5 +12,7 @@ def all_libraries() -> list:
         {"name": "alofa_sampling", "sources": ["kernels/sampling.cu"]},
         {"name": "alofa_gemm_tc", "sources": ["kernels/gemm_tc.cu"]},
         {"name": "alofa_elementwise_bf16", "sources": ["kernels/elementwise_bf16.cu"]},
+        # latent attention on tensor cores is built per latent size at first use; the size of the tests' model is built ahead
+        {"name": "alofa_latent_attention_kv64_r32", "sources": ["kernels/latent_attention_bf16.cu"], "defines": {"KV_RANK": 64, "ROT": 32}},
         *[{"name": f"alofa_attention_hd{hd}", "sources": ["kernels/attention_bf16.cu"], "defines": {"HEAD_DIM": hd}} for hd in (16, 32, 48, 64, 128)],
     ]

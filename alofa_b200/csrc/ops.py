@@ -714,3 +714,43 @@ def moe_combine(y, ys, dest, weight, shared, gate, top: int) -> None:
                                     y.shape[0], top, y.shape[1], _stream()),
         "moe_combine",
     )
+
+
+def latent_attention_bf16_supported(kv_rank: int, rot: int) -> bool:
+    """Latent sizes the tensor-core kernel is built for (one library per size,
+    compiled at first use): whole 16-column MMA tiles for each half of the
+    value columns and for the row width, accumulators that fit the registers,
+    tiles that fit shared memory."""
+    width = kv_rank + rot
+    return kv_rank % 32 == 0 and width % 16 == 0 and 32 <= kv_rank <= 512 and 128 * (width + 8) * 2 <= 220 * 1024
+
+
+def _latent_attention_lib(kv_rank: int, rot: int):
+    key = f"latent_attention_kv{kv_rank}_r{rot}"
+    lib = _libs.get(key)
+    if lib is None:
+        lib = load_library(f"alofa_{key}", ["kernels/latent_attention_bf16.cu"], defines={"KV_RANK": kv_rank, "ROT": rot})
+        lib.alofa_latent_attention_bf16.restype = _I
+        lib.alofa_latent_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]
+        _libs[key] = lib
+    return lib
+
+
+def latent_attention_bf16(out, qa, cache_rows, sink, q_start, kv_len, block_table, page_size: int, n_seqs: int, max_q_len: int, heads: int, kv_rank: int, rot: int,
+                          window, scale: float) -> None:
+    """The same attention as :func:`latent_attention` on tensor cores, for
+    bfloat16 and sizes :func:`latent_attention_bf16_supported` names: the rows
+    of request r are ``q_start[r] .. q_start[r + 1]``, the last of them at
+    position ``kv_len[r] - 1``."""
+    bf = torch.bfloat16
+    n = qa.shape[0]
+    if qa.shape[1] != heads * (kv_rank + rot) or tuple(out.shape) != (n, heads * kv_rank) or cache_rows.shape[1] != kv_rank + rot:
+        raise AlofaError("invalid_argument", "latent_attention sizes disagree", f"qa={tuple(qa.shape)} out={tuple(out.shape)} cache={tuple(cache_rows.shape)}")
+    _done(
+        _latent_attention_lib(kv_rank, rot).alofa_latent_attention_bf16(
+            _dev(out, "out", bf), _dev(qa, "qa", bf), _dev(cache_rows, "cache", bf), _dev(sink, "sink", torch.float32) if sink is not None else None,
+            _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
+            page_size, n_seqs, max_q_len, heads, int(window or 0), float(scale), _stream(),
+        ),
+        "latent_attention_bf16", f"heads={heads} kv_rank={kv_rank} rot={rot}",
+    )

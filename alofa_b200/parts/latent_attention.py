@@ -128,6 +128,13 @@ class LatentAttention(Part):
             h.add_(y)
 
     def attend(self, ctx, o_lat, qa, cache, group):
+        """Attention of the step's rows over the cached latent rows: on tensor
+        cores for bfloat16 and sizes that kernel is built for, else the kernel
+        that takes every size."""
+        if qa.dtype == torch.bfloat16 and ops.latent_attention_bf16_supported(self.kv_rank, self.rot):
+            ops.latent_attention_bf16(o_lat, qa, cache.k, self.sink, ctx.q_start, ctx.kv_len, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
+                                      self.heads, self.kv_rank, self.rot, self.window, self.scale)
+            return
         ops.latent_attention(o_lat, qa, cache.k, self.sink, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
                              self.heads, self.kv_rank, self.rot, self.window, self.scale)
 

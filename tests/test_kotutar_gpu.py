@@ -1,0 +1,482 @@
+"""Kotutar on the GPU against the plain implementation (tests/plain_kotutar.py).
+
+Mechanisms alone (kernel against the plain function of the same mechanism):
+the latent rows and their rotation, queries carried into the latent space,
+attention over paged latent rows (sink, far keys, page borders, a window's
+edges, more heads than one block takes), sandwich norms, the router and the
+routed feed-forward's bookkeeping, the mix-in of the embedding output.  Then
+whole models of three configurations, in 32-bit and bfloat16: whole prompts,
+prefill against token-by-token decoding, portions down to two tokens, batches
+of unequal requests in a pool so small that pages and slots are used again, long
+decoding from the first token, and greedy generation through the engine, its
+scheduler and the command-line programs."""
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_kotutar as plain
+import replay
+import tiny_kotutar as tiny
+from gpu_util import assert_close, dev, paged_from_sequences, rounded
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+# Largest |engine - plain| on logits, times max(1, max|plain|): fp32 sums against float64; bfloat16
+# rounds activations and cache rows to 8 bits of mantissa (set from the worst seen).
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+KERNEL_TOL = {F32: 1e-5, BF16: 2e-2}
+
+
+# ---------------------------------------------------------------------------------------------------
+# mechanisms alone
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("q_rank,kv_rank,rot,dims", [(40, 48, 8, 8), (7, 130, 12, 6), (64, 64, 0, 0)])
+def test_latent_rows_are_normed_turned_and_stored(dtype, q_rank, kv_rank, rot, dims):
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(1)
+    n, eps, base = 9, 3e-5, 700.0
+    lat = rng.standard_normal((n, q_rank + kv_rank + rot)) * 3.0
+    wq, wkv = 1 + 0.2 * rng.standard_normal(q_rank), 1 + 0.2 * rng.standard_normal(kv_rank)
+    positions = np.array([0, 1, 2, 63, 64, 65, 500, 4095, 100000], dtype=np.int32)
+    slots = rng.permutation(32)[:n].astype(np.int32)
+    freq = (base ** (-2.0 * np.arange(max(dims // 2, 1)) / max(dims, 1))).astype(np.float32)
+    cq = torch.empty((n, q_rank), dtype=dtype, device="cuda")
+    cache = torch.full((32, kv_rank + rot), 9.0, dtype=dtype, device="cuda")
+    ops.latent_prepare(cq, cache, dev(lat, F32), dev(wq, F32), dev(wkv, F32), dev(freq), dev(positions), dev(slots), q_rank, kv_rank, rot, dims, eps)
+    lat32 = rounded(lat, F32)
+    assert_close(cq.float().cpu(), plain.rms(lat32[:, :q_rank], rounded(wq, F32), eps), KERNEL_TOL[dtype], "c_q")
+    want = np.concatenate([plain.rms(lat32[:, q_rank : q_rank + kv_rank], rounded(wkv, F32), eps),
+                           plain.turn_pairs(lat32[:, q_rank + kv_rank :], positions, base, dims)], axis=-1)
+    got = cache.float().cpu().numpy()
+    # angles are fp32 in the kernel: at position p the angle carries an error of about p * 6e-8
+    tol = max(KERNEL_TOL[dtype], 2e-7 * float(positions.max()) * (1 if dims else 0))
+    assert_close(got[slots], want, tol, "cache rows")
+    untouched = np.setdiff1d(np.arange(32), slots)
+    assert (got[untouched] == 9.0).all(), "a row of another slot was written"
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_queries_carried_into_the_latent_space_score_like_per_head_keys(dtype):
+    """qa . [c | kr] = q . Wuk_h c + turned(qr) . kr for every head."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(2)
+    n, heads, dim, rot, dims, kv_rank, base = 6, 5, 24, 8, 8, 40, 1e4
+    q = rounded(rng.standard_normal((n, heads, dim + rot)), dtype)
+    uk = rounded(rng.standard_normal((heads * dim, kv_rank)) / 5, dtype)
+    positions = np.array([0, 3, 64, 129, 1000, 77], dtype=np.int32)
+    freq = (base ** (-2.0 * np.arange(dims // 2) / dims)).astype(np.float32)
+    uk_t = dev(uk.reshape(heads, dim, kv_rank).transpose(0, 2, 1), dtype)
+    qa = torch.zeros((n, heads * (kv_rank + rot)), dtype=dtype, device="cuda")
+    qd = dev(q.reshape(n, -1), dtype)
+    ops.latent_query_turn(qa, qd, dev(freq), dev(positions), heads, dim, rot, dims, kv_rank)
+    ops.gemm_batched(qa, qd, uk_t, heads, n, kv_rank, dim, heads * (dim + rot), dim + rot, dim, kv_rank * dim, heads * (kv_rank + rot), kv_rank + rot)
+    got = qa.float().cpu().numpy().reshape(n, heads, kv_rank + rot)
+    row = rng.standard_normal((kv_rank + rot,))
+    for h in range(heads):
+        want = q[:, h, :dim] @ (uk[h * dim : (h + 1) * dim] @ row[:kv_rank]) + plain.turn_pairs(q[:, h, dim:], positions, base, dims) @ row[kv_rank:]
+        assert_close(got[:, h] @ row, want, 4 * KERNEL_TOL[dtype], f"head {h}")
+
+
+def latent_case(rng, lengths, heads, kv_rank, rot, dtype, page=16):
+    """Random latent rows per request in a paged cache with scattered pages, and one query per token."""
+    width = kv_rank + rot
+    rows = [rounded(rng.standard_normal((n, width)), dtype) for n in lengths]
+    cache, _, table = paged_from_sequences(rows, rows, page, 1, width, dtype, rng)
+    qa = [rounded(rng.standard_normal((n, heads, width)) / np.sqrt(width), dtype) for n in lengths]
+    return rows, cache.view(-1, width), table, qa
+
+
+def plain_latent_attention(qa, rows, sink, kv_rank, scale, window=None):
+    n = len(rows)
+    i, j = np.arange(n)[:, None], np.arange(n)[None, :]
+    seen = (j <= i) & ((j > i - window) if window else True)
+    out = np.zeros((n, qa.shape[1], kv_rank))
+    for h in range(qa.shape[1]):
+        s = np.where(seen, qa[:, h] @ rows.T * scale, -np.inf)
+        out[:, h] = plain.softmax_with_sink(s, sink[h] if sink is not None else -np.inf) @ rows[:, :kv_rank]
+    return out
+
+
+def run_latent_attention(qa, rows, cache, table, sink, lengths, heads, kv_rank, rot, scale, dtype, window=None, page=16, last_only=False):
+    """Every token of every request in one launch (or only the last token of each: decoding)."""
+    from alofa_b200.csrc import ops
+
+    picks = [[n - 1] if last_only else list(range(n)) for n in lengths]
+    q = np.concatenate([qa[r][picks[r]] for r in range(len(lengths))]).reshape(-1, heads * (kv_rank + rot))
+    positions = np.concatenate([np.array(p, dtype=np.int32) for p in picks])
+    seq = np.concatenate([np.full(len(p), r, dtype=np.int32) for r, p in enumerate(picks)])
+    out = torch.empty((len(q), heads * kv_rank), dtype=dtype, device="cuda")
+    ops.latent_attention(out, dev(q, dtype), cache, dev(sink, F32) if sink is not None else None, dev(positions), dev(seq), table, page, heads, kv_rank, rot, window, scale)
+    return out.float().cpu().numpy().reshape(-1, heads, kv_rank), picks
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("heads,kv_rank,rot,window", [(3, 48, 8, None), (10, 20, 4, None), (8, 64, 32, 37), (1, 130, 0, 16)])
+def test_latent_attention_over_paged_rows(dtype, heads, kv_rank, rot, window):
+    """Prompts and decoding, lengths at page borders (16) and chunk borders (32), a sink per head; with a
+    window also its edges."""
+    rng = np.random.default_rng(3)
+    lengths = [1, 2, 15, 16, 17, 31, 32, 33, 64, 65, 150]
+    rows, cache, table, qa = latent_case(rng, lengths, heads, kv_rank, rot, dtype)
+    sink = rng.standard_normal(heads)
+    scale = 1.7
+    want = [plain_latent_attention(qa[r], rows[r], rounded(sink, F32), kv_rank, scale, window) for r in range(len(lengths))]
+    for last_only in (False, True):
+        got, picks = run_latent_attention(qa, rows, cache, table, sink, lengths, heads, kv_rank, rot, scale, dtype, window, last_only=last_only)
+        at = 0
+        for r, p in enumerate(picks):
+            assert_close(got[at : at + len(p)], want[r][p], KERNEL_TOL[dtype], f"request {r} ({lengths[r]} rows), decoding={last_only}")
+            at += len(p)
+
+
+def run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv_rank, rot, scale, window=None, page=16):
+    """The tensor-core kernel on the last ``portions[r]`` tokens of every request, all in one launch."""
+    from alofa_b200.csrc import ops
+
+    q = np.concatenate([qa[r][n - k : n] for r, (n, k) in enumerate(zip(lengths, portions))]).reshape(-1, heads * (kv_rank + rot))
+    q_start = np.concatenate([[0], np.cumsum(portions)]).astype(np.int32)
+    out = torch.empty((len(q), heads * kv_rank), dtype=BF16, device="cuda")
+    ops.latent_attention_bf16(out, dev(q, BF16), cache, dev(sink, F32) if sink is not None else None, dev(q_start), dev(np.array(lengths, dtype=np.int32)), table, page,
+                              len(lengths), max(portions), heads, kv_rank, rot, window, scale)
+    return out.float().cpu().numpy().reshape(-1, heads, kv_rank), q_start
+
+
+@pytest.mark.parametrize("heads,kv_rank,rot,window,sunk", [(3, 64, 16, None, True), (10, 32, 16, 37, True), (16, 128, 32, None, False), (5, 96, 0, 16, True), (70, 32, 0, None, True)])
+def test_latent_attention_on_tensor_cores(heads, kv_rank, rot, window, sunk):
+    """Whole prompts, portions that end a longer history (2 tokens, a page and a bit), and single decode
+    tokens, at lengths around the borders of pages (16), key blocks (32) and row tiles (64 rows of
+    (token, head)), against the plain softmax with sink."""
+    from alofa_b200.csrc import ops
+
+    assert ops.latent_attention_bf16_supported(kv_rank, rot)
+    rng = np.random.default_rng(8)
+    lengths = [1, 2, 15, 16, 17, 31, 32, 33, 63, 64, 65, 97, 150]
+    rows, cache, table, qa = latent_case(rng, lengths, heads, kv_rank, rot, BF16)
+    sink = rng.standard_normal(heads) if sunk else None
+    want = [plain_latent_attention(qa[r], rows[r], rounded(sink, F32) if sunk else None, kv_rank, 1.3, window) for r in range(len(lengths))]
+    for what, portions in (("whole", lengths), ("decode", [1] * len(lengths)), ("two", [min(2, n) for n in lengths]), ("tail", [min(21, n) for n in lengths])):
+        got, q_start = run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv_rank, rot, 1.3, window)
+        for r, (n, k) in enumerate(zip(lengths, portions)):
+            assert_close(got[q_start[r] : q_start[r + 1]], want[r][n - k : n], KERNEL_TOL[BF16], f"{what}: request {r} ({n} rows, last {k})")
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_one_far_key_among_hundreds_and_the_sink(dtype):
+    """A query made to match ONE row far back: the output must be that row's latent (whichever page and
+    chunk holds it); with a sink far above every score the output vanishes; with a window that ends one
+    row after the match the match is gone."""
+    rng = np.random.default_rng(4)
+    heads, kv_rank, rot, n = 2, 32, 16, 700
+    width = kv_rank + rot
+    rows, cache, table, qa = latent_case(rng, [n], heads, kv_rank, rot, dtype)
+    for far in (0, 1, 15, 16, 31, 32, 333, 639, 640, 698):
+        q = [qa[0].copy()]
+        q[0][n - 1, :] = rounded(rows[0][far] * 3.0, dtype)  # score about 3 |row|^2 = 120, all others about 0 +- 20
+        got, _ = run_latent_attention(q, rows, cache, table, np.zeros(heads), [n], heads, kv_rank, rot, 1.0, dtype, last_only=True)
+        assert_close(got[0, 0], rows[0][far][:kv_rank], 5e-2 if dtype == BF16 else 1e-4, f"match at row {far}")
+        off = n - 1 - far  # a window of `off` rows ends one row after the match, `off + 1` just reaches it
+        if off > 0:
+            inside, _ = run_latent_attention(q, rows, cache, table, np.zeros(heads), [n], heads, kv_rank, rot, 1.0, dtype, window=off + 1, last_only=True)
+            assert_close(inside[0, 0], rows[0][far][:kv_rank], 5e-2 if dtype == BF16 else 1e-4, f"window just reaches row {far}")
+            outside, _ = run_latent_attention(q, rows, cache, table, np.zeros(heads), [n], heads, kv_rank, rot, 1.0, dtype, window=off, last_only=True)
+            assert np.abs(outside[0, 0] - rows[0][far][:kv_rank]).max() > 0.5, f"window of {off} rows still sees row {far}"
+        sunk, _ = run_latent_attention(q, rows, cache, table, np.array([400.0, -400.0]), [n], heads, kv_rank, rot, 1.0, dtype, last_only=True)
+        assert np.abs(sunk[0, 0]).max() < 1e-6 and np.abs(sunk[0, 1] - rows[0][far][:kv_rank]).max() < 6e-2
+        if dtype == BF16:  # the same through the tensor-core kernel: decoding, and as the end of a portion of 40 tokens
+            for portion in (1, 40):
+                tc, _ = run_latent_attention_tc(q, cache, table, np.zeros(heads), [n], [portion], heads, kv_rank, rot, 1.0)
+                assert_close(tc[-1, 0], rows[0][far][:kv_rank], 5e-2, f"tensor cores: match at row {far}")
+                if off > 0:
+                    tc, _ = run_latent_attention_tc(q, cache, table, np.zeros(heads), [n], [portion], heads, kv_rank, rot, 1.0, window=off + 1)
+                    assert_close(tc[-1, 0], rows[0][far][:kv_rank], 5e-2, f"tensor cores: window just reaches row {far}")
+                    tc, _ = run_latent_attention_tc(q, cache, table, np.zeros(heads), [n], [portion], heads, kv_rank, rot, 1.0, window=off)
+                    assert np.abs(tc[-1, 0] - rows[0][far][:kv_rank]).max() > 0.5, f"tensor cores: window of {off} rows still sees row {far}"
+            tc, _ = run_latent_attention_tc(q, cache, table, np.array([400.0, -400.0]), [n], [1], heads, kv_rank, rot, 1.0)
+            assert np.abs(tc[0, 0]).max() < 1e-6 and np.abs(tc[0, 1] - rows[0][far][:kv_rank]).max() < 6e-2
+
+
+def test_sandwich_norm_adds_and_norms_ahead():
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(5)
+    for hidden in (96, 100, 1):
+        h, y = rng.standard_normal((7, hidden)) * 4, rng.standard_normal((7, hidden)) * 0.01
+        wp, wn = 1 + 0.3 * rng.standard_normal(hidden), 1 + 0.3 * rng.standard_normal(hidden)
+        hd, x = dev(h, F32), torch.empty((7, hidden), dtype=BF16, device="cuda")
+        ops.sandwich_norm(hd, dev(y, F32), dev(wp, F32), 1e-5, x, dev(wn, F32), 2e-6)
+        want = rounded(h, F32) + plain.rms(rounded(y, F32), rounded(wp, F32), 1e-5)
+        assert_close(hd.cpu(), want, 1e-6, "stream")
+        assert_close(x.float().cpu(), plain.rms(want, rounded(wn, F32), 2e-6), 1e-2, "norm ahead")
+        h2 = dev(h, F32)
+        ops.sandwich_norm(h2, dev(y, F32), dev(wp, F32), 1e-5)
+        assert torch.equal(h2, hd)
+
+
+@pytest.mark.parametrize("experts,top", [(5, 2), (12, 1), (7, 7), (40, 3)])
+def test_router_sort_scatter_and_combine(experts, top):
+    """Scores and choices against the plain router; the sorted matrix holds every pair once, experts in
+    ascending order on whole tiles; scatter and combine are inverse to one another."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(6)
+    n, hidden, tile = 37, 24, ops.MOE_TILE
+    x = rounded(rng.standard_normal((n, hidden)), F32)
+    wr = rounded(rng.standard_normal((experts + 1, hidden)), F32)
+    z = dev(x @ wr.T, F32)
+    choice, weight = torch.empty((n, top), dtype=torch.int32, device="cuda"), torch.empty((n, top), dtype=F32, device="cuda")
+    gate = torch.empty((n,), dtype=F32, device="cuda")
+    ops.moe_route(choice, weight, gate, z, experts, top)
+    want_choice, want_weight = plain.router(x, {"router": wr[:experts]}, "", top)
+    assert (choice.cpu().numpy() == want_choice).all()
+    assert_close(weight.cpu(), want_weight, 1e-6, "weights")
+    assert_close(gate.cpu(), 1 / (1 + np.exp(-(x @ wr[experts]))), 1e-6, "shared gate")
+    tiles = -(-n * top // tile) + experts
+    dest, tile_expert = torch.empty((n, top), dtype=torch.int32, device="cuda"), torch.empty((tiles,), dtype=torch.int32, device="cuda")
+    ops.moe_sort(dest, tile_expert, choice, experts, tile)
+    d, te = dest.cpu().numpy().ravel(), tile_expert.cpu().numpy()
+    assert len(set(d.tolist())) == n * top and d.max() < tiles * tile
+    assert (te[d // tile] == want_choice.ravel()).all(), "a pair lies on a tile of another expert"
+    used = te[te >= 0]
+    assert (np.diff(used) >= 0).all() and (te[len(used):] == -1).all()
+    xs = torch.zeros((tiles * tile, hidden), dtype=F32, device="cuda")
+    ops.moe_scatter(xs, dev(x, F32), weight, dest, top)
+    assert_close(xs.cpu().numpy()[d], (x[:, None, :] * want_weight[:, :, None]).reshape(n * top, hidden), 1e-6, "scattered rows")
+    y = torch.empty((n, hidden), dtype=F32, device="cuda")
+    shared = rounded(rng.standard_normal((n, hidden)), F32)
+    ops.moe_combine(y, xs, dest, None, dev(shared, F32), gate, top)
+    assert_close(y.cpu(), x * want_weight.sum(-1, keepdims=True) + shared / (1 + np.exp(-(x @ wr[experts])))[:, None], 1e-5, "combined")
+
+
+def test_interleaved_rotation_in_place_and_the_activations():
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((5, 3, 12))
+    positions = np.array([0, 1, 70, 4000, 12], dtype=np.int32)
+    freq = (50.0 ** (-2.0 * np.arange(4) / 8)).astype(np.float32)
+    xd = dev(x, F32)
+    ops.rotary_interleaved(xd, dev(freq), dev(positions), 3, 12, 8)
+    assert_close(xd.cpu(), plain.turn_pairs(rounded(x, F32), positions, 50.0, 8), 1e-3, "turned pairs")
+    z = rng.standard_normal((4, 10)) * 3
+    b = rng.standard_normal(10)
+    for act, fn in (("gelu_erf", plain.gelu_erf), ("gelu_tanh", plain.gelu_tanh)):
+        out = torch.empty((4, 10), dtype=F32, device="cuda")
+        ops.activate(out, dev(z, F32), dev(b, F32), act)
+        assert_close(out.cpu(), fn(rounded(z, F32) + rounded(b, F32)), 1e-6, act)
+
+
+# ---------------------------------------------------------------------------------------------------
+# whole models
+# ---------------------------------------------------------------------------------------------------
+LENGTHS = {"A": [1, 2, 23, 64, 65, 129, 200], "B": [3, 63, 128, 131], "C": [5, 64, 190, 257]}
+DECODED = 12
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = tmp_path_factory.mktemp("kotutar_gpu")
+    return {name: tiny.write(base / name, name, seed=10 + i) for i, name in enumerate(tiny.CONFIGS)}
+
+
+def make_requests(name):
+    reqs, prompts = {}, {}
+    for i, n in enumerate(LENGTHS[name]):
+        reqs[f"r{i}"] = tiny.tokens(name, n + DECODED, seed=i)
+        prompts[f"r{i}"] = n
+    return reqs, prompts
+
+
+@pytest.fixture(scope="module")
+def plain_logits(folders):
+    """name -> (request -> logits, request -> positions before the first close call of a router)."""
+    out = {}
+    for name, folder in folders.items():
+        w, cfg = plain.load(folder)
+        logits, sure = {}, {}
+        for rid, toks in make_requests(name)[0].items():
+            margins = []
+            logits[rid] = plain.forward(toks, w, cfg, margins=margins)
+            sure[rid] = plain.sure_prefix(margins, len(toks))
+        out[name] = (logits, sure)
+    return out
+
+
+def runner_for(folder, dtype, block, pages, max_requests=8, graphs=True):
+    from alofa_b200.engine.loading import load_model
+    from alofa_b200.engine.step import StepRunner
+
+    model, *_ = load_model(folder, dtype)
+    return StepRunner(model, block_size=block, num_pages=pages, max_requests=max_requests, max_tokens=pages * block, max_step_tokens=512, cuda_graphs=graphs)
+
+
+def compare(steps, outputs, want, vocab, tol, what, sure=None):
+    """Every position within ``tol``.  ``sure`` (bfloat16): request -> how many leading positions precede
+    its first close call of a router.  A routed feed-forward is not continuous: where two experts' scores
+    lie within rounding, bfloat16 may rightly choose the other, and that position and, through the cache,
+    those after it then differ by more than rounding (measured: 1 % of difference in the activations moves
+    a score by up to 0.03, and a flipped position differs by 0.2 to 0.5).  So in bfloat16 the bound is strict
+    up to the first close call; over all positions nine tenths must keep it and the median a third of it
+    (a wrong key, page or state moves every position).  In 32-bit every position is held to it."""
+    got = replay.collect(steps, outputs, vocab)
+    errors = []
+    for rid, rows in got.items():
+        ref = want[rid][: len(rows)]
+        assert rows.shape == ref.shape, f"{what} {rid}: {rows.shape} vs {ref.shape}"
+        err = np.abs(rows - ref).max(axis=-1) / max(1.0, float(np.abs(ref).max()))
+        n = len(rows) if sure is None else min(len(rows), sure[rid])
+        if n:
+            assert err[:n].max() <= tol, f"{what} {rid}: position {int(err[:n].argmax())} differs by {err[:n].max():.3e} > {tol:.1e}"
+        errors.append(err)
+    errors = np.concatenate(errors)
+    assert_most_close(errors, tol, what)
+    return errors
+
+
+def assert_most_close(errors, tol, what):
+    errors = np.asarray(errors)
+    assert (errors > tol).mean() <= 0.1 and np.median(errors) <= tol / 3, \
+        f"{what}: {(errors > tol).sum()} of {len(errors)} positions beyond {tol:.1e}, median {np.median(errors):.3e}, worst {errors.max():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_whole_decoded_portions_and_mixed_batches(folders, plain_logits, name, dtype):
+    """The same requests whole, with the last tokens decoded one by one, in portions down to two tokens,
+    and mixed (portions beside single tokens, four live at most) in a pool that holds two of the longest:
+    pages and slots are given back and used again.  Every position against plain."""
+    reqs, prompts = make_requests(name)
+    vocab = tiny.CONFIGS[name]["vocab"]
+    block = 16 if name == "B" else 64
+    per_request = -(-max(len(t) for t in reqs.values()) // block)
+    schedules = {
+        "whole": (replay.whole(reqs), per_request),
+        "decoded": (replay.tail_decoded(reqs, tail=DECODED + 20), per_request),
+        "portions": (replay.portions(reqs), per_request),
+        "mixed": (replay.mixed(reqs, prompts, 2 * per_request * block + block, block, seed=3), 2 * per_request + 1),
+    }
+    for what, (steps, pages) in schedules.items():
+        runner = runner_for(folders[name], dtype, block, pages, max_requests=4)
+        out = replay.run_inprocess(runner, steps)
+        compare(steps, out, plain_logits[name][0], vocab, TOL[dtype], f"{name}/{dtype}/{what}", sure=plain_logits[name][1] if dtype == "bfloat16" else None)
+        assert runner.manager.free_pages() == [pages] and runner.manager.live_requests() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_from_the_first_token(folders, dtype):
+    """One prompt token, then 150 tokens one by one (past two page borders of 64 and many chunk borders),
+    two requests side by side that started 40 steps apart; decode steps are replayed as graphs."""
+    from alofa_b200.engine.step import StepEntry
+
+    name = "A"
+    w, cfg = plain.load(folders[name])
+    a, b = tiny.tokens(name, 151, seed=50), tiny.tokens(name, 111, seed=51)
+    ma, mb = [], []
+    want_a, want_b = plain.forward(a, w, cfg, margins=ma), plain.forward(b, w, cfg, margins=mb)
+    sure_a, sure_b = (plain.sure_prefix(ma, 151), plain.sure_prefix(mb, 111)) if dtype == "bfloat16" else (151, 111)
+    runner = runner_for(folders[name], dtype, 64, 5, max_requests=2)
+    sa = runner.admit(0)
+    sb, errors = None, []
+    for i in range(151):
+        entries = [StepEntry(sa, [a[i]], [0])]
+        if i >= 40:
+            if sb is None:
+                sb = runner.admit(1)
+            entries.append(StepEntry(sb, [b[i - 40]], [0]))
+        rows = runner.forward(entries).float().cpu().numpy()
+        # bfloat16: strict up to a router's first close call, most positions after it (see compare)
+        for row, want, k, sure, who in ((rows[0], want_a, i, sure_a, "first"),) + (((rows[1], want_b, i - 40, sure_b, "second"),) if i >= 40 else ()):
+            if k < sure:
+                assert_close(row, want[k], TOL[dtype], f"{who} request, token {k}")
+            errors.append(np.abs(row - want[k]).max() / max(1.0, float(np.abs(want).max())))
+    assert_most_close(errors, TOL[dtype], "long decoding")
+    runner.check_status()
+    assert runner.manager.defects() == 0
+
+
+def test_batches_do_not_change_a_request(folders):
+    """float32: a request's logits in a mixed batch equal, to rounding of the sums' order, those it gets alone."""
+    name = "B"
+    reqs, prompts = make_requests(name)
+    vocab = tiny.CONFIGS[name]["vocab"]
+    alone = replay.collect(replay.whole(reqs), replay.run_inprocess(runner_for(folders[name], "float32", 16, 10), replay.whole(reqs)), vocab)
+    steps = replay.mixed(reqs, prompts, 400, 16, seed=9)
+    together = replay.collect(steps, replay.run_inprocess(runner_for(folders[name], "float32", 16, 25), steps), vocab)
+    for rid in reqs:
+        assert np.abs(alone[rid] - together[rid]).max() <= 2e-6 * max(1.0, np.abs(alone[rid]).max()), rid
+
+
+def test_the_stream_after_every_layer_run(folders):
+    """float32: the residual stream after each run of a layer (looped layers count each time)."""
+    import alofa_b200.parts.block as block
+    from alofa_b200.engine.step import StepEntry
+
+    name = "A"
+    w, cfg = plain.load(folders[name])
+    ids = tiny.tokens(name, 30, seed=77)
+    want = []
+    plain.forward(ids, w, cfg, stream=want)
+    seen, original = [], block.SandwichResidual.forward
+
+    def recording(self, ctx, h, cache, writes=True):
+        original(self, ctx, h, cache, writes)
+        seen.append(h.clone())
+
+    block.SandwichResidual.forward = recording
+    try:
+        runner = runner_for(folders[name], "float32", 64, 1, graphs=False)
+        runner.forward([StepEntry(runner.admit(0), ids, [0])])
+    finally:
+        block.SandwichResidual.forward = original
+    assert len(seen) == len(want) == 5
+    for k, (got, ref) in enumerate(zip(seen, want)):
+        assert_close(got.cpu(), ref, 1e-5, f"after layer run {k}")
+
+
+@pytest.mark.parametrize("name", list(tiny.CONFIGS))
+def test_greedy_generation_through_the_engine(folders, name):
+    """Engine.generate (scheduler, chunked prefill, decode graphs): float32 tokens equal plain greedy;
+    bfloat16 tokens are each within rounding of the plain maximum."""
+    from alofa_b200.engine.engine import Engine
+
+    w, cfg = plain.load(folders[name])
+    prompts = [tiny.tokens(name, n, seed=200 + i) for i, n in enumerate([1, 7, 40, 90, 18])]
+    want = [plain.greedy(p, 6, w, cfg) for p in prompts]
+    eng = Engine(str(folders[name]), dtype="float32", block_size=16, max_batch=3, token_budget=48, max_chunk=32, max_tokens=128)
+    assert eng.generate(prompts, max_new_tokens=6) == want
+    assert eng.stats()["defects"] == 0
+    eng16 = Engine(str(folders[name]), dtype="bfloat16", block_size=16, max_batch=3, token_budget=48, max_chunk=32, max_tokens=128)
+    for p, out in zip(prompts, eng16.generate(prompts, max_new_tokens=6)):
+        seq = list(p)
+        for tok in out:
+            margins = []
+            row = plain.forward(seq, w, cfg, margins=margins)[-1]
+            if plain.sure_prefix(margins, len(seq)) < len(seq):
+                break  # a router's close call: from here on bfloat16 may rightly go another way
+            assert row.max() - row[tok] <= 8e-2 * max(1.0, float(np.abs(row).max())), "a bfloat16 token is not near the plain maximum"
+            seq.append(tok)
+    eng16.runner.check_status()
+
+
+def test_the_programs_take_the_architecture(folders, tmp_path):
+    """bin/trace_run replays a schedule and bin/generate generates, both choosing the model by config.json."""
+    name = "C"
+    reqs, _ = make_requests(name)
+    reqs = {k: reqs[k] for k in ("r0", "r2")}
+    w, cfg = plain.load(folders[name])
+    want = {rid: plain.forward(t, w, cfg) for rid, t in reqs.items()}
+    steps = replay.portions(reqs, sizes=(40, 2, 3, 64, 1))
+    out = replay.run_trace_program(folders[name], "float32", steps, tmp_path / "out", 512)
+    compare(steps, out, want, cfg["vocab"], TOL["float32"], "trace_run")
+    prompt = tiny.tokens(name, 12, seed=5)
+    done = subprocess.run([sys.executable, str(replay.ROOT / "bin" / "generate"), "--model", str(folders[name]), "--dtype", "float32", "--prompt-ids",
+                           ",".join(map(str, prompt)), "--max-new-tokens", "5", "--max-tokens", "64", "--json"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert json.loads(done.stdout.strip().splitlines()[-1])["out_ids"] == [plain.greedy(prompt, 5, w, cfg)]
