@@ -50,6 +50,19 @@ __device__ __forceinline__ float silu_times(float g, float u) {
   return g * r * u;
 }
 
+// Activations that an epilogue may apply to its fp32 sums (after the bias): the precise library
+// functions, the same in every kernel that takes an activation code.
+enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU = 4 };
+__device__ __forceinline__ float activate(float z, int act) {
+  switch (act) {
+    case ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));  // the exact gelu: z Phi(z)
+    case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    case ACT_SILU: return z / (1.0f + expf(-z));
+    case ACT_RELU: return fmaxf(z, 0.f);
+    default: return z;
+  }
+}
+
 // Sum over a warp in a fixed butterfly order; every lane gets the result.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -63,6 +63,7 @@ struct GemmArgs {
   int T, N, K;        // tokens, output features (GATED: per half), depth
   int k_slices_per_split;
   int out_bf16;
+  int act;            // EPI_STORE: an activation on the sums plus bias (codes of common.cuh), 0 for none
   int pair;           // tokens on M: the wide product runs on pairs of CTAs (the weight map's box is then 128 rows)
   int few;            // tokens on M, persistent, up to 64 tokens: the token map's box is this many rows (32 or 64), else 0
   int* status;
@@ -475,7 +476,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
           else ((float*)args.out)[(size_t)t * args.N + f] = y;
         } else {
-          const float y = a0 + bias0;
+          const float y = activate(a0 + bias0, EPI == EPI_STORE ? args.act : 0);
           if (args.out_bf16) ((bf16*)args.out)[(size_t)t * args.N + f] = __float2bfloat16_rn(y);
           else ((float*)args.out)[(size_t)t * args.N + f] = y;
         }
@@ -692,6 +693,7 @@ __device__ __forceinline__ void tokens_epilogue_staged(const GemmArgs& args, uin
           if (args.bias && f + j < N) u += args.bias[N + f + j];
           a = silu_times(a, u);
         }
+        if (EPI == EPI_STORE && !split && args.act) a = activate(a, args.act);
         v[j] = a;
       }
 #pragma unroll
@@ -903,6 +905,10 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         if (GATED) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = silu_times(v[j], u[j]);
+        }
+        if (EPI == EPI_STORE && args.act) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = activate(v[j], args.act);
         }
         if (EPI == EPI_RESIDUAL) {
           float* o = (float*)args.out + (size_t)t * N + f;
@@ -1260,7 +1266,7 @@ gemm_tc_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 // ---------------------------------------------------------------------------
 template <int EPI>
 __global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __restrict__ partial, const float* __restrict__ bias, int T, int N,
-                                     int splits, int out_bf16) {
+                                     int splits, int out_bf16, int act) {
   constexpr int N_ACC = (EPI == EPI_GATED) ? 2 : 1;
   const size_t plane = (size_t)T * N;
   pdl_begin();
@@ -1287,6 +1293,7 @@ __global__ void splitk_reduce_kernel(void* __restrict__ out, const float* __rest
     if (N_ACC == 2) a1 += bias[N + f];
   }
   float y = a0;
+  if (EPI == EPI_STORE && act) y = activate(a0, act);
   if (EPI == EPI_GATED) y = silu_times(a0, a1);
   if (EPI == EPI_RESIDUAL) {
     ((float*)out)[idx] += y;
@@ -1577,6 +1584,9 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
                             const int* b_positions, int b_heads, int b_head_dim, int b_window, int b_split_keys, long long* acc,
                             const long long* n_acc, const float* n_gamma, float n_eps, float* n_out, long long* n_zero, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
+  const int act = epi >> 4;  // EPI_STORE | (code << 4): an activation on the sums plus bias
+  epi &= 15;
+  if (act && (epi != EPI_STORE || b_kind != B_ROWS)) return ALOFA_ERR_ARGUMENT;
   if (acc && (epi != EPI_RESIDUAL || bn <= 0)) return ALOFA_ERR_ARGUMENT;
   if (b_kind == B_NORMED) {
     if (bn != 16 || T > 16 || epi != EPI_GATED || !b_src || !n_gamma || !n_out || n_out == b_src || (K % 8) != 0 || !do_reduce) return ALOFA_ERR_ARGUMENT;
@@ -1620,6 +1630,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   args.k_slices_per_split = (total_slices + splits - 1) / splits;
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
+  args.act = act;
   args.pair = pair ? 1 : 0;
   args.few = few;
   args.status = status;
@@ -1653,9 +1664,9 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
-  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
-  else launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
+  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
+  else launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
   return launch_status();
 }
 
@@ -1664,13 +1675,15 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
 ALOFA_API int alofa_splitk_reduce(void* out, const float* partial, const float* bias, int T, int N, int splits, int epi, int out_bf16,
                                   cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
+  const int act = epi >> 4;
+  epi &= 15;
   if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
   const size_t plane = (size_t)T * N;
   const int threads = 256;
   const unsigned blocks = (unsigned)((plane + threads - 1) / threads);
-  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
-  else if (epi == EPI_GATED) launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16);
+  if (epi == EPI_STORE) launch_dep(splitk_reduce_kernel<EPI_STORE>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
+  else if (epi == EPI_RESIDUAL) launch_dep(splitk_reduce_kernel<EPI_RESIDUAL>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
+  else if (epi == EPI_GATED) launch_dep(splitk_reduce_kernel<EPI_GATED>, blocks, threads, 0, stream, out, partial, bias, T, N, splits, out_bf16, act);
   else return ALOFA_ERR_ARGUMENT;
   return launch_status();
 }

@@ -79,6 +79,7 @@ ALOFA_API int alofa_rmsnorm(void* out, const void* x, const void* w, const int* 
 //   EPI_STORE    out[m, n] = acc
 //   EPI_RESIDUAL out[m, n] += acc        (out is the fp32 residual stream)
 //   EPI_GATED    W holds [gate; up] (2N rows): out[m, n] = silu(gate) * up
+// EPI_STORE | (code << 4): out[m, n] = act(acc + bias), the activation codes of common.cuh.
 // 64x64 tile, 16-deep slices, 256 threads with 4x4 outputs each; every output
 // is summed by one thread over k ascending.
 // ---------------------------------------------------------------------------
@@ -87,7 +88,7 @@ enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED = 2 };
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256) gemm_generic_kernel(TO* __restrict__ out, const TA* __restrict__ x,
                                                            const TW* __restrict__ w, const float* __restrict__ bias, int M,
-                                                           int N, int K) {
+                                                           int N, int K, int act) {
   constexpr int BM = 64, BN = 64, BK = 16;
   constexpr int NW = (EPI == EPI_GATED) ? 2 : 1;
   __shared__ float xs[BK][BM + 1];
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(TO* __restrict__ out,
         if (EPI == EPI_RESIDUAL)
           out[o] = from_f<TO>(to_f(out[o]) + v);
         else
-          out[o] = from_f<TO>(v);
+          out[o] = from_f<TO>(activate(v, act));
       }
     }
   }
@@ -165,13 +166,16 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(TO* __restrict__ out,
 template <typename TA, typename TW, typename TO>
 static int gemm_generic_launch(void* out, const void* x, const void* w, const float* bias, int M, int N, int K, int epi,
                                cudaStream_t stream) {
+  const int act = epi >> 4;  // EPI_STORE only: an activation on the sums (codes of common.cuh)
+  epi &= 15;
+  if (act && epi != EPI_STORE) return ALOFA_ERR_ARGUMENT;
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   if (epi == EPI_STORE)
-    gemm_generic_kernel<TA, TW, TO, EPI_STORE><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K);
+    gemm_generic_kernel<TA, TW, TO, EPI_STORE><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K, act);
   else if (epi == EPI_RESIDUAL)
-    gemm_generic_kernel<TA, TW, TO, EPI_RESIDUAL><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K);
+    gemm_generic_kernel<TA, TW, TO, EPI_RESIDUAL><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K, act);
   else if (epi == EPI_GATED)
-    gemm_generic_kernel<TA, TW, TO, EPI_GATED><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K);
+    gemm_generic_kernel<TA, TW, TO, EPI_GATED><<<grid, 256, 0, stream>>>((TO*)out, (const TA*)x, (const TW*)w, bias, M, N, K, act);
   else
     return ALOFA_ERR_ARGUMENT;
   return launch_status();
@@ -183,7 +187,7 @@ ALOFA_API int alofa_gemm_generic(void* out, const void* x, const void* w, const 
                                  int x_bf16, int w_bf16, int out_bf16, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return ALOFA_OK;
   if (K <= 0) return ALOFA_ERR_ARGUMENT;
-  if (epi == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
+  if ((epi & 15) == EPI_RESIDUAL && out_bf16) return ALOFA_ERR_ARGUMENT;
   const float* b = (const float*)bias;
   const int key = (x_bf16 ? 4 : 0) | (w_bf16 ? 2 : 0) | (out_bf16 ? 1 : 0);
   switch (key) {

@@ -164,18 +164,6 @@ ALOFA_API int alofa_rotary_interleaved(void* x, const float* freq, const int* po
 // tile is empty): rows sorted by expert, each expert's rows padded to whole tiles.
 // 64x64 tile, 16-deep slices, every output summed by one thread over k ascending.
 // ---------------------------------------------------------------------------
-enum { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU = 4 };
-
-__device__ __forceinline__ float activate(float z, int act) {
-  switch (act) {
-    case ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
-    case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-    case ACT_SILU: return z / (1.0f + expf(-z));
-    case ACT_RELU: return fmaxf(z, 0.f);
-    default: return z;
-  }
-}
-
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256) gemm_batched_kernel(TO* __restrict__ out, const TA* __restrict__ x, const TW* __restrict__ w,
                                                            const float* __restrict__ bias, const int* __restrict__ tile_batch, int M, int N, int K,

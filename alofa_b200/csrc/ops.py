@@ -8,6 +8,7 @@ loaded raises when it is first needed."""
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -223,8 +224,9 @@ def rmsnorm(out, x, weight, eps: float, rows=None) -> None:
     )
 
 
-def gemm_generic(out, x, w, bias, epi: int) -> None:
-    """out = x @ w.T (+bias) with the epilogue ``epi``; any sizes."""
+def gemm_generic(out, x, w, bias, epi: int, act: int = 0) -> None:
+    """out = x @ w.T (+bias) with the epilogue ``epi``; any sizes.  ``act``
+    (EPI_STORE only): a code of ``ACTIVATIONS`` applied to the fp32 sums."""
     m, k = x.shape
     n = out.shape[1]
     rows_w = 2 * n if epi == EPI_GATED else n
@@ -233,7 +235,7 @@ def gemm_generic(out, x, w, bias, epi: int) -> None:
     _done(
         _generic().alofa_gemm_generic(
             _dev(out, "out"), _dev(x, "x"), _dev(w, "w"), _dev(bias, "bias", torch.float32) if bias is not None else None,
-            m, n, k, epi, _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
+            m, n, k, epi | (act << 4), _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
         ),
         "gemm_generic", f"M={m} N={n} K={k} epi={epi}",
     )
@@ -341,7 +343,7 @@ def gemm_tc_splits(k: int, splits: int) -> int:
 B_ROWS, B_MERGED_SPLITS, B_NORMED = 0, 1, 2
 
 
-def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None, acc=None) -> bool:
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None, acc=None, act: int = 0) -> bool:
     """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
     the epilogue fused.  Returns False, having launched nothing, when the
     kernel does not take these sizes (depth not a multiple of 8, unaligned).
@@ -356,7 +358,10 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
 
     ``acc`` (residual products, weights on M): the sums are added into this
     int64 accumulator ``[tokens, features]`` (units of 2^-32) with atomic adds
-    instead of into ``out``; nothing else is written."""
+    instead of into ``out``; nothing else is written.
+
+    ``act`` (EPI_STORE only): a code of ``ACTIVATIONS`` applied to the fp32
+    sums plus bias before they are stored."""
     n = out.shape[1]
     rows_w = 2 * n if epi == EPI_GATED else n
     k = w.shape[1]
@@ -383,7 +388,7 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
         _dev(out, "out"), _dev(x, "x", torch.bfloat16) if x is not None else None, _dev(w, "w", torch.bfloat16),
         _dev(bias, "bias", f32) if bias is not None else None,
         _dev(partial, "partial", f32) if partial is not None else None,
-        m, n, k, epi, _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
+        m, n, k, epi | (act << 4), _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
         _dev(status, "status", torch.int32) if status is not None else None,
         b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys,
         _dev(acc, "acc", i64) if acc is not None else None, n_acc, n_gamma, float(n_eps), n_out, n_zero, _stream(),
@@ -537,12 +542,13 @@ _L = ctypes.c_longlong
 def _latent():
     lib = _libs.get("latent")
     if lib is None:
-        lib = load_library("alofa_latent", ["kernels/latent.cu"])
+        lib = load_library("alofa_latent", ["kernels/latent.cu", "kernels/gemm_batched_bf16.cu"])
         sigs = {
             "alofa_latent_prepare": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
             "alofa_latent_query_turn": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rotary_interleaved": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
             "alofa_gemm_batched": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _P],
+            "alofa_gemm_batched_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _P],
             "alofa_activate": [_P, _P, _P, _L, _I, _I, _I, _P],
             "alofa_latent_attention": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
             "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
@@ -614,10 +620,24 @@ def gemm_batched(out, x, w, batches: int, m: int, n: int, k: int, ldx: int, x_ba
     b, operands addressed by row and batch strides (in elements) from the
     tensors' first elements.  With ``tile_batch`` (int32, one entry per 64-row
     tile) there is one x and one out and tile i uses the weight of batch
-    ``tile_batch[i]``; negative entries are skipped."""
+    ``tile_batch[i]``; negative entries are skipped.  bfloat16 operands whose
+    depth and strides are multiples of 8 go to the tensor-core kernel, all
+    others to the one that takes every size."""
     for t, name in ((out, "out"), (x, "x"), (w, "w")):
         if not t.is_cuda:
             raise AlofaError("unsupported", "kernels run on CUDA tensors only", f"{name} is on {t.device}")
+    bf = torch.bfloat16
+    if (x.dtype == bf and w.dtype == bf and not (k % 8 or ldx % 8 or ldw % 8 or x_batch % 8 or w_batch % 8 or x.data_ptr() % 16 or w.data_ptr() % 16)
+            and os.environ.get("ALOFA_BATCHED_TC", "1") != "0"):
+        _done(
+            _latent().alofa_gemm_batched_bf16(
+                out.data_ptr(), x.data_ptr(), w.data_ptr(), _dev(bias, "bias", torch.float32) if bias is not None else None,
+                _dev(tile_batch, "tile_batch", torch.int32) if tile_batch is not None else None, batches, m, n, k, ldx, x_batch, ldw, w_batch, ldo, out_batch,
+                bias_batch, ACTIVATIONS[act], _is_bf16(out, "out"), _stream(),
+            ),
+            "gemm_batched_bf16", f"batches={batches} M={m} N={n} K={k}",
+        )
+        return
     _done(
         _latent().alofa_gemm_batched(
             out.data_ptr(), x.data_ptr(), w.data_ptr(), _dev(bias, "bias", torch.float32) if bias is not None else None,

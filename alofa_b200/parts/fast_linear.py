@@ -89,7 +89,7 @@ def plan(linear):
         lazy = None if isinstance(x, torch.Tensor) else x
         if lazy is not None:
             x = None
-        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1))
+        splits = ops.gemm_tc_splits(depth, _splits(_ctas(tokens, linear.out_features, bn, gated), depth, defer and n_acc == 1 and not linear.act))
         computed = None
         if lazy is not None:
             # Rows still to be made.  The weights-on-M kernel makes them as it loads, a k-slice at a
@@ -109,9 +109,9 @@ def plan(linear):
         if splits > 1 and acc is None and not normed:
             shape = (splits * n_acc, tokens, linear.out_features)
             partial = buf(shape, torch.float32) if buf is not None else torch.empty(shape, dtype=torch.float32, device=w.device)
-        deferred = defer and splits > 1 and n_acc == 1 and acc is None
+        deferred = defer and splits > 1 and n_acc == 1 and acc is None and not linear.act  # whoever adds deferred sums up applies no activation
         dst = partial[0] if deferred else out  # a deferred product writes partial sums only
-        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed, acc=acc):
+        if not ops.gemm_tc(dst, x, w, linear.bias, linear.epi, bn, splits, partial, reduce=not deferred, computed=computed, acc=acc, act=linear.act):
             if normed:
                 lazy.undo()
                 return run(out, lazy.rows(), defer, buf)

@@ -80,19 +80,16 @@ class DenseMLP(Part):
 
     def load(self, state):
         pre = self.prefix
-        self.up_bias = as_float32_vector(state[pre + "up.b"]) if self.bias else None
-        self.up = Linear(state[pre + "up"], None, STORE)
+        self.up = Linear(state[pre + "up"], as_float32_vector(state[pre + "up.b"]) if self.bias else None, STORE, act=self.act)
         self.down = Linear(state[pre + "down"], as_float32_vector(state[pre + "down.b"]) if self.bias else None, STORE)
 
     def scratch_row_bytes(self) -> int:
-        return 8 * self.inter + 4 * self.hidden
+        return 4 * self.inter + 4 * self.hidden
 
     def forward(self, ctx, x, h, store=False):
         n = x.shape[0]
-        sums = ctx.buf((n, self.inter), torch.float32)
-        self.up(sums, x, buf=ctx.buf)
         mid = ctx.buf((n, self.inter), self.rt.dtype)
-        ops.activate(mid, sums, self.up_bias, self.act)
+        self.up(mid, x, buf=ctx.buf)  # bias and activation on the fp32 sums, in the product's epilogue
         if store:
             self.down(h, mid, buf=ctx.buf)
         else:

@@ -108,13 +108,17 @@ ACCUMULATED = object()  # what a residual product returns when it added its sums
 
 
 class Linear:
-    """``epi`` STORE: out = x W^T + b.  RESIDUAL: out (fp32) += x W^T + b.
-    GATED: W = [gate; up]: out = silu(x Wg^T) * (x Wu^T)."""
+    """``epi`` STORE: out = act(x W^T + b), ``act`` a name of
+    ``ops.ACTIVATIONS`` taken on the fp32 sums.  RESIDUAL: out (fp32) += x W^T
+    + b.  GATED: W = [gate; up]: out = silu(x Wg^T) * (x Wu^T)."""
 
-    def __init__(self, weight: torch.Tensor, bias, epi: int = STORE):
+    def __init__(self, weight: torch.Tensor, bias, epi: int = STORE, act: str = "none"):
         self.weight = weight.contiguous()
         self.bias = bias
         self.epi = epi
+        self.act = ops.ACTIVATIONS[act]
+        if self.act and epi != STORE:
+            raise AlofaError("invalid_argument", "only a stored product takes an activation", f"epi={epi} act={act}")
         rows, self.in_features = self.weight.shape
         if epi == GATED and rows % 2:
             raise AlofaError("invalid_argument", "a gated weight needs an even number of rows", f"rows={rows}")
@@ -150,7 +154,7 @@ class Linear:
                 return done if isinstance(done, Partial) else None
         if not isinstance(x, torch.Tensor):
             x = x.rows()
-        ops.gemm_generic(out, x, self.weight, self.bias, self.epi)
+        ops.gemm_generic(out, x, self.weight, self.bias, self.epi, self.act)
         return None
 
 
