@@ -433,11 +433,76 @@ __global__ void __launch_bounds__(256) sandwich_norm_kernel(float* __restrict__ 
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) x[r + c] = from_f<T>(h[r + c] * g * w_next[c]);
 }
 
+// The same with the row in registers (hidden a multiple of 4, at most 4 * 256 * CHUNKS): every element
+// of y and h is read once, 16 bytes a thread, and h and x are written once.  The sums run over the same
+// elements per thread and the same block reduction as above only when the sizes agree, so a size goes
+// one way or the other for every row of every step.
+template <typename T, int CHUNKS>
+__global__ void __launch_bounds__(256) sandwich_norm_rows_kernel(float* __restrict__ h, const float* __restrict__ y, const float* __restrict__ w_post,
+                                                                 float eps_post, T* __restrict__ x, const float* __restrict__ w_next, float eps_next,
+                                                                 int hidden) {
+  __shared__ float scratch[32];
+  pdl_begin();
+  const size_t r = (size_t)blockIdx.x * hidden;
+  const int quads = hidden >> 2;
+  float4 yv[CHUNKS], hv[CHUNKS];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = threadIdx.x + 256 * i;
+    if (c < quads) {
+      yv[i] = reinterpret_cast<const float4*>(y + r)[c];
+      hv[i] = reinterpret_cast<const float4*>(h + r)[c];
+      ss = fmaf(yv[i].x, yv[i].x, fmaf(yv[i].y, yv[i].y, fmaf(yv[i].z, yv[i].z, fmaf(yv[i].w, yv[i].w, ss))));
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float f = 1.0f / sqrtf(ss / (float)hidden + eps_post);
+  float s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = threadIdx.x + 256 * i;
+    if (c < quads) {
+      const float4 w = reinterpret_cast<const float4*>(w_post)[c];
+      hv[i] = make_float4(hv[i].x + yv[i].x * f * w.x, hv[i].y + yv[i].y * f * w.y, hv[i].z + yv[i].z * f * w.z, hv[i].w + yv[i].w * f * w.w);
+      reinterpret_cast<float4*>(h + r)[c] = hv[i];
+      s2 = fmaf(hv[i].x, hv[i].x, fmaf(hv[i].y, hv[i].y, fmaf(hv[i].z, hv[i].z, fmaf(hv[i].w, hv[i].w, s2))));
+    }
+  }
+  if (!x) return;
+  s2 = block_sum(s2, scratch);
+  const float g = 1.0f / sqrtf(s2 / (float)hidden + eps_next);
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = threadIdx.x + 256 * i;
+    if (c < quads) {
+      const float4 w = reinterpret_cast<const float4*>(w_next)[c];
+      T* o = x + r + 4 * (size_t)c;
+      o[0] = from_f<T>(hv[i].x * g * w.x);
+      o[1] = from_f<T>(hv[i].y * g * w.y);
+      o[2] = from_f<T>(hv[i].z * g * w.z);
+      o[3] = from_f<T>(hv[i].w * g * w.w);
+    }
+  }
+}
+
+template <typename T>
+static void sandwich_norm_launch(float* h, const float* y, const float* w_post, float eps_post, T* x, const float* w_next, float eps_next, int rows,
+                                 int hidden, cudaStream_t stream) {
+  const bool aligned = (hidden & 3) == 0 && !(((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)w_next) & 15);
+  if (aligned && hidden <= 4 * 256 * 2)
+    launch_dep(sandwich_norm_rows_kernel<T, 2>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+  else if (aligned && hidden <= 4 * 256 * 8)
+    launch_dep(sandwich_norm_rows_kernel<T, 8>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+  else
+    launch_dep(sandwich_norm_kernel<T>, rows, 256, 0, stream, h, y, w_post, eps_post, x, w_next, eps_next, hidden);
+}
+
 ALOFA_API int alofa_sandwich_norm(float* h, const float* y, const float* w_post, float eps_post, void* x, const float* w_next, float eps_next,
                                   int rows, int hidden, int x_bf16, cudaStream_t stream) {
   if (rows <= 0) return ALOFA_OK;
-  if (x_bf16) launch_dep(sandwich_norm_kernel<bf16>, rows, 256, 0, stream, h, y, w_post, eps_post, (bf16*)x, w_next, eps_next, hidden);
-  else launch_dep(sandwich_norm_kernel<float>, rows, 256, 0, stream, h, y, w_post, eps_post, (float*)x, w_next, eps_next, hidden);
+  if (x_bf16) sandwich_norm_launch<bf16>(h, y, w_post, eps_post, (bf16*)x, w_next, eps_next, rows, hidden, stream);
+  else sandwich_norm_launch<float>(h, y, w_post, eps_post, (float*)x, w_next, eps_next, rows, hidden, stream);
   return launch_status();
 }
 
@@ -515,6 +580,81 @@ __global__ void moe_route_kernel(int* __restrict__ choice, float* __restrict__ w
   if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zr[E]));
 }
 
+// The router's product and the choice in one kernel: z = x Wr^T in fp32 (x in the compute dtype, Wr fp32
+// [E (+1), hidden]), one warp per token: every lane sums its share of the depth for one expert at a
+// time, the warp adds the shares in butterfly order (the order depends on the sizes alone), the logits
+// stay in shared memory for the choice above.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate,
+                                                         const T* __restrict__ x, const float* __restrict__ wr, int T_, int E, int top, int hidden,
+                                                         int gated, int softmax, int renormalize) {
+  extern __shared__ float sc[];  // [8 warps][E + 1]
+  pdl_begin();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  if (t >= T_) return;
+  float* s = sc + warp * (E + 1);
+  const T* xr = x + (size_t)t * hidden;
+  const int cols = E + (gated ? 1 : 0);
+  for (int e = 0; e < cols; ++e) {
+    const float* w = wr + (size_t)e * hidden;
+    float dot = 0.f;
+    for (int c = lane; c < hidden; c += 32) dot = fmaf(to_f(xr[c]), w[c], dot);
+    dot = warp_sum(dot);
+    if (lane == 0) s[e] = dot;
+  }
+  __syncwarp();
+  const float zg = gated ? s[E] : 0.f;
+  if (softmax) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      s[e] = expf(s[e] - mx);
+      sum += s[e];
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) s[e] /= sum;
+  } else {
+    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+  }
+  __syncwarp();
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (s[e] > best) best = s[e], arg = e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+    }
+    if (arg >= E) arg = k, best = 0.f;
+    if (lane == 0) {
+      choice[(size_t)t * top + k] = arg;
+      weight[(size_t)t * top + k] = best;
+      s[arg] = -INFINITY;
+    }
+    total += best;
+    __syncwarp();
+  }
+  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+  if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zg));
+}
+
+ALOFA_API int alofa_moe_router(int* choice, float* weight, float* gate, const void* x, const float* wr, int T, int E, int top, int hidden, int softmax,
+                               int renormalize, int x_bf16, cudaStream_t stream) {
+  if (T <= 0) return ALOFA_OK;
+  if (E <= 0 || top <= 0 || top > E || top > 32 || (size_t)8 * (E + 1) * 4 > 48 * 1024) return ALOFA_ERR_ARGUMENT;
+  const size_t smem = (size_t)8 * (E + 1) * sizeof(float);
+  if (x_bf16) launch_dep(moe_router_kernel<bf16>, (T + 7) / 8, 256, smem, stream, choice, weight, gate, (const bf16*)x, wr, T, E, top, hidden, gate ? 1 : 0, softmax, renormalize);
+  else launch_dep(moe_router_kernel<float>, (T + 7) / 8, 256, smem, stream, choice, weight, gate, (const float*)x, wr, T, E, top, hidden, gate ? 1 : 0, softmax, renormalize);
+  return launch_status();
+}
+
 ALOFA_API int alofa_moe_route(int* choice, float* weight, float* gate, const float* z, int T, int E, int top, int cols, int softmax, int renormalize,
                               cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
@@ -557,9 +697,77 @@ __global__ void moe_sort_kernel(int* __restrict__ dest, int* __restrict__ tile_e
   }
 }
 
+// The same result faster, for as many experts as shared memory holds a count per thread for: thread i
+// takes the pairs [i * share, (i + 1) * share), counts them per expert, the counts of each expert are
+// summed over the threads in thread order (so the order within an expert stays the order of the pairs),
+// and every thread numbers its pairs from there.
+constexpr int SORT_THREADS = 256;
+__global__ void __launch_bounds__(SORT_THREADS) moe_sort_counted_kernel(int* __restrict__ dest, int* __restrict__ tile_expert, const int* __restrict__ choice,
+                                                                        int pairs, int E, int tile, int max_tiles) {
+  extern __shared__ int counted[];  // [E][SORT_THREADS] counts, then offsets; then [E] first rows
+  pdl_begin();
+  int* first = counted + E * SORT_THREADS;
+  const int tid = threadIdx.x;
+  const int share = (pairs + SORT_THREADS - 1) / SORT_THREADS;
+  const int lo = min(pairs, tid * share), hi = min(pairs, lo + share);
+  for (int e = 0; e < E; ++e) counted[e * SORT_THREADS + tid] = 0;
+  for (int i = lo; i < hi; ++i) counted[choice[i] * SORT_THREADS + tid] += 1;
+  __syncthreads();
+  // an exclusive sum over the threads, per expert: a warp takes experts in turn, a lane eight threads' counts
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int e = warp; e < E; e += SORT_THREADS / 32) {
+    int* row = counted + e * SORT_THREADS;
+    int v[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] = row[lane * 8 + j];
+      sum += v[j];
+    }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    int at = incl - sum;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      row[lane * 8 + j] = at;
+      at += v[j];
+    }
+    if (lane == 31) first[e] = incl;  // the expert's count, for now
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      const int n = first[e], tiles = (n + tile - 1) / tile;
+      first[e] = at;
+      for (int i = 0; i < tiles; ++i) tile_expert[at / tile + i] = e;
+      at += tiles * tile;
+    }
+    for (int i = at / tile; i < max_tiles; ++i) tile_expert[i] = -1;
+  }
+  __syncthreads();
+  for (int i = lo; i < hi; ++i) {
+    const int e = choice[i];
+    dest[i] = first[e] + counted[e * SORT_THREADS + tid]++;
+  }
+}
+
 ALOFA_API int alofa_moe_sort(int* dest, int* tile_expert, const int* choice, int pairs, int E, int tile, int max_tiles, cudaStream_t stream) {
   if (pairs <= 0) return ALOFA_OK;
   if (E <= 0 || tile <= 0 || (size_t)2 * E * 4 > 48 * 1024 || max_tiles < (pairs + tile - 1) / tile) return ALOFA_ERR_ARGUMENT;
+  const size_t counted = ((size_t)E * SORT_THREADS + E) * sizeof(int);
+  if (counted <= 200 * 1024) {
+    static size_t set = 0;
+    if (counted > set) {
+      if (cudaFuncSetAttribute(moe_sort_counted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)counted) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+      set = counted;
+    }
+    launch_dep(moe_sort_counted_kernel, 1, SORT_THREADS, counted, stream, dest, tile_expert, choice, pairs, E, tile, max_tiles);
+    return launch_status();
+  }
   launch_dep(moe_sort_kernel, 1, 256, (size_t)2 * E * sizeof(int), stream, dest, tile_expert, choice, pairs, E, tile, max_tiles);
   return launch_status();
 }

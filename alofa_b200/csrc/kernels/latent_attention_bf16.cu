@@ -19,6 +19,11 @@
 //
 // Causal bound and window go by the row's own position; keys past the request's
 // length are never fetched (their rows in shared memory are zeroed).
+//
+// Decode steps split each request's key blocks over grid.z CTAs (a request alone
+// is one CTA per 64 rows, far fewer than there are SMs): every split leaves its
+// normalised output, maximum and sum in fp32, the sink enters in split 0 only,
+// and a second kernel merges the splits in split order.
 #include "common.cuh"
 
 #ifndef KV_RANK
@@ -33,7 +38,9 @@ namespace {
 constexpr int D = KV_RANK + ROT;
 constexpr int PITCH = D + 8;          // elements per row in shared memory: 16 bytes of padding keep ldmatrix off bank conflicts
 constexpr int BM = 64, BN = 32;
+constexpr int STAGES = 3;             // key blocks in flight per CTA
 constexpr int THREADS = 256;
+constexpr int MIN_CTAS = KV_RANK <= 256 ? 2 : 1;  // the output accumulators are KV_RANK / 4 registers a thread
 constexpr int HALF = KV_RANK / 2;     // value columns per warp
 constexpr int NT = HALF / 8;          // n-tiles of the output per warp
 static_assert(KV_RANK % 32 == 0 && D % 16 == 0, "latent sizes this kernel takes");
@@ -58,13 +65,14 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa, const bf16* __restrict__ cache, const float* __restrict__ sink,
                              const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_blocks,
-                             int page_size, int heads, int window, float scale_log2) {
+                             int page_size, int heads, int window, float scale_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
+                             int blocks_per_split, int total_rows) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][PITCH]
-  bf16* Ks = Qs + BM * PITCH;                        // [2][BN][PITCH]
+  bf16* Ks = Qs + BM * PITCH;                        // [STAGES][BN][PITCH]
   pdl_begin();
   const int seq = blockIdx.y, tile = blockIdx.x;
   const int t0 = q_start[seq], q_len = q_start[seq + 1] - t0;
@@ -92,7 +100,12 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
   const int key_hi = pos0 + last_row / heads;  // inclusive
   int key_lo = 0;
   if (window > 0) key_lo = max(0, pos0 + r0 / heads - window + 1);
-  const int b_lo = key_lo / BN, b_hi = key_hi / BN;
+  int b_lo = key_lo / BN, b_hi = key_hi / BN;
+  const bool split = gridDim.z > 1;
+  if (split) {  // this CTA's share of the key blocks (it may be empty)
+    b_lo = max(b_lo, (int)blockIdx.z * blocks_per_split);
+    b_hi = min(b_hi, ((int)blockIdx.z + 1) * blocks_per_split - 1);
+  }
 
   auto fetch = [&](int b, int buf) {
     bf16* dst = Ks + (size_t)buf * BN * PITCH;
@@ -108,8 +121,11 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
       }
     }
   };
-  fetch(b_lo, 0);
-  cp_commit();
+#pragma unroll
+  for (int st = 0; st < STAGES - 1; ++st) {
+    if (b_lo + st <= b_hi) fetch(b_lo + st, st);
+    cp_commit();
+  }
 
   // this thread's two rows of its group: g and g + 8
   int pos[2], first[2];
@@ -120,7 +136,7 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
     const bool live = r < rows;
     pos[i] = live ? pos0 + r / heads : -1;
     first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
-    const bool sunk = live && sink != nullptr;
+    const bool sunk = live && sink != nullptr && blockIdx.z == 0;
     m[i] = sunk ? sink[r % heads] * 1.4426950408889634f : -INFINITY;
     l[i] = sunk ? 1.f : 0.f;
   }
@@ -132,10 +148,10 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
 
   const uint32_t q_base = smem_addr(Qs + (rg * 16 + (lane & 15)) * PITCH + (lane >> 4) * 8);
   for (int b = b_lo; b <= b_hi; ++b) {
-    const int buf = (b - b_lo) & 1;
-    if (b < b_hi) fetch(b + 1, buf ^ 1);
+    const int buf = (b - b_lo) % STAGES;
+    if (b + STAGES - 1 <= b_hi) fetch(b + STAGES - 1, (b - b_lo + STAGES - 1) % STAGES);  // into the buffer of the block before this one, read out
     cp_commit();
-    cp_wait<1>();
+    cp_wait<STAGES - 1>();
     __syncthreads();
     const bf16* Kb = Ks + (size_t)buf * BN * PITCH;
     // S = Q K^T for 16 rows x 32 keys
@@ -220,10 +236,37 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
     const int r = r0 + rg * 16 + g + 8 * i;
     if (r >= rows) continue;
     const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    if (split) {
+      const size_t row = (size_t)blockIdx.z * total_rows + (size_t)t0 * heads + r;
+      float* dst = part_o + row * KV_RANK + ch * HALF + 2 * t;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) *reinterpret_cast<float2*>(dst + j * 8) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+      if (ch == 0 && t == 0) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m[i], l[i]);
+      continue;
+    }
     bf16* dst = out + ((size_t)t0 * heads + r) * KV_RANK + ch * HALF + 2 * t;
 #pragma unroll
     for (int j = 0; j < NT; ++j)
       *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+  }
+}
+
+// out[row] = sum_z w_z o_z / sum_z w_z with w_z = l_z 2^(m_z - max m), splits in ascending order.
+__global__ void latent_attention_merge_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
+                                              int total_rows) {
+  pdl_begin();
+  const size_t row = blockIdx.x;
+  float top = -INFINITY;
+  for (int z = 0; z < splits; ++z) top = fmaxf(top, part_ml[((size_t)z * total_rows + row) * 2]);
+  for (int c = threadIdx.x; c < KV_RANK; c += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float2 ml = *reinterpret_cast<const float2*>(part_ml + ((size_t)z * total_rows + row) * 2);
+      const float w = ml.y > 0.f ? ml.y * exp2f(ml.x - top) : 0.f;
+      num = fmaf(w, part_o[((size_t)z * total_rows + row) * KV_RANK + c], num);
+      den += w;
+    }
+    out[row * KV_RANK + c] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
   }
 }
 
@@ -233,10 +276,13 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
 // step (or, for a recorded step, the longest it may hold).
 ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void* cache, const float* sink, const int* q_start, const int* kv_len,
                                           const int* block_table, int max_blocks, int page_size, int n_seqs, int max_q_len, int heads, int window,
-                                          float scale, cudaStream_t stream) {
+                                          float scale, float* part_o, float* part_ml, int splits, int blocks_per_split, int total_rows,
+                                          cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0) return ALOFA_OK;
   if (heads <= 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
-  const size_t smem = (size_t)(BM + 2 * BN) * PITCH * sizeof(bf16);
+  if (splits < 1) splits = 1;
+  if (splits > 1 && (!part_o || !part_ml || blocks_per_split <= 0 || total_rows <= 0 || splits > 65535)) return ALOFA_ERR_ARGUMENT;
+  const size_t smem = (size_t)(BM + STAGES * BN) * PITCH * sizeof(bf16);
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(latent_attention_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
@@ -244,13 +290,15 @@ ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void*
   }
   const long long tiles = ((long long)max_q_len * heads + BM - 1) / BM;
   if (tiles > 2147483647LL || n_seqs > 65535) return ALOFA_ERR_ARGUMENT;
-  launch_dep(latent_attention_bf16_kernel, dim3((unsigned)tiles, n_seqs), dim3(THREADS), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache, sink,
-             q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f);
+  launch_dep(latent_attention_bf16_kernel, dim3((unsigned)tiles, n_seqs, splits), dim3(THREADS), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache,
+             sink, q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f, part_o, part_ml, blocks_per_split,
+             total_rows);
+  if (splits > 1) launch_dep(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (bf16*)out, part_o, part_ml, splits, total_rows);
   return launch_status();
 }
 
 ALOFA_API int alofa_latent_attention_bf16_sizes(int* kv_rank, int* rot) {
   *kv_rank = KV_RANK;
   *rot = ROT;
-  return (int)((BM + 2 * BN) * PITCH * sizeof(bf16));
+  return (int)((BM + STAGES * BN) * PITCH * sizeof(bf16));
 }

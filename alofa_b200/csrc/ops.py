@@ -554,6 +554,7 @@ def _latent():
             "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
             "alofa_concat_rows": [_P, _P, _P, _I, _I, _I, _P],
             "alofa_moe_route": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_moe_sort": [_P, _P, _P, _I, _I, _I, _I, _P],
             "alofa_moe_scatter": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
             "alofa_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -711,6 +712,20 @@ def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = F
     )
 
 
+def moe_router(choice, weight, gate, x, wr, experts: int, top: int, softmax: bool = False, renormalize: bool = False) -> None:
+    """:func:`moe_route` with the router's product in the same kernel: ``x``
+    [T, hidden] in the compute dtype, ``wr`` fp32 [experts (+1 with ``gate``),
+    hidden]; logits and scores are fp32."""
+    i32, f32 = torch.int32, torch.float32
+    if wr.shape != (experts + (1 if gate is not None else 0), x.shape[1]):
+        raise AlofaError("invalid_argument", "router sizes disagree", f"wr={tuple(wr.shape)} x={tuple(x.shape)} experts={experts}")
+    _done(
+        _latent().alofa_moe_router(_dev(choice, "choice", i32), _dev(weight, "weight", f32), _dev(gate, "gate", f32) if gate is not None else None, _dev(x, "x"),
+                                   _dev(wr, "wr", f32), x.shape[0], experts, top, x.shape[1], 1 if softmax else 0, 1 if renormalize else 0, _is_bf16(x, "x"), _stream()),
+        "moe_router", f"experts={experts} top={top}",
+    )
+
+
 def moe_sort(dest, tile_expert, choice, experts: int, tile: int = MOE_TILE) -> None:
     """Rows of the (token, choice) pairs in a matrix sorted by expert, every
     expert padded to whole tiles: ``dest`` [pairs], ``tile_expert`` [tiles]."""
@@ -742,7 +757,7 @@ def latent_attention_bf16_supported(kv_rank: int, rot: int) -> bool:
     value columns and for the row width, accumulators that fit the registers,
     tiles that fit shared memory."""
     width = kv_rank + rot
-    return kv_rank % 32 == 0 and width % 16 == 0 and 32 <= kv_rank <= 512 and 128 * (width + 8) * 2 <= 220 * 1024
+    return kv_rank % 32 == 0 and width % 16 == 0 and 32 <= kv_rank <= 512 and (64 + 3 * 32) * (width + 8) * 2 <= 220 * 1024
 
 
 def _latent_attention_lib(kv_rank: int, rot: int):
@@ -751,17 +766,24 @@ def _latent_attention_lib(kv_rank: int, rot: int):
     if lib is None:
         lib = load_library(f"alofa_{key}", ["kernels/latent_attention_bf16.cu"], defines={"KV_RANK": kv_rank, "ROT": rot})
         lib.alofa_latent_attention_bf16.restype = _I
-        lib.alofa_latent_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]
+        lib.alofa_latent_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _I, _P]
         _libs[key] = lib
     return lib
 
 
+LATENT_KEY_BLOCK = 32  # rows of the cache per key block of the tensor-core kernel
+
+
 def latent_attention_bf16(out, qa, cache_rows, sink, q_start, kv_len, block_table, page_size: int, n_seqs: int, max_q_len: int, heads: int, kv_rank: int, rot: int,
-                          window, scale: float) -> None:
+                          window, scale: float, splits: int = 1, blocks_per_split: int = 0, part_o=None, part_ml=None) -> None:
     """The same attention as :func:`latent_attention` on tensor cores, for
     bfloat16 and sizes :func:`latent_attention_bf16_supported` names: the rows
     of request r are ``q_start[r] .. q_start[r + 1]``, the last of them at
-    position ``kv_len[r] - 1``."""
+    position ``kv_len[r] - 1``.  With ``splits`` > 1 every request's key
+    blocks (of ``LATENT_KEY_BLOCK`` rows) are dealt to that many CTAs,
+    ``blocks_per_split`` each, which leave their shares in ``part_o`` [splits,
+    T * heads, kv_rank] and ``part_ml`` [splits, T * heads, 2] (fp32) for a
+    second kernel to merge."""
     bf = torch.bfloat16
     n = qa.shape[0]
     if qa.shape[1] != heads * (kv_rank + rot) or tuple(out.shape) != (n, heads * kv_rank) or cache_rows.shape[1] != kv_rank + rot:
@@ -770,7 +792,11 @@ def latent_attention_bf16(out, qa, cache_rows, sink, q_start, kv_len, block_tabl
         _latent_attention_lib(kv_rank, rot).alofa_latent_attention_bf16(
             _dev(out, "out", bf), _dev(qa, "qa", bf), _dev(cache_rows, "cache", bf), _dev(sink, "sink", torch.float32) if sink is not None else None,
             _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.shape[1],
-            page_size, n_seqs, max_q_len, heads, int(window or 0), float(scale), _stream(),
+            page_size, n_seqs, max_q_len, heads, int(window or 0), float(scale),
+            _dev(part_o, "part_o", torch.float32) if splits > 1 else None, _dev(part_ml, "part_ml", torch.float32) if splits > 1 else None,
+            splits, blocks_per_split, n * heads, _stream(),
         ),
-        "latent_attention_bf16", f"heads={heads} kv_rank={kv_rank} rot={rot}",
+        "latent_attention_bf16", f"heads={heads} kv_rank={kv_rank} rot={rot} splits={splits}",
     )
+    if splits > 1:
+        count_launches(1)

@@ -21,6 +21,7 @@ import torch
 
 from ..csrc import ops
 from ..errors import AlofaError
+from . import fast_linear
 from .base import PagedRows, Part, TensorSpec, as_float32_vector, build_part, register_part
 from .linear import STORE, Linear
 
@@ -132,8 +133,21 @@ class LatentAttention(Part):
         cores for bfloat16 and sizes that kernel is built for, else the kernel
         that takes every size."""
         if qa.dtype == torch.bfloat16 and ops.latent_attention_bf16_supported(self.kv_rank, self.rot):
+            splits, per_split, part_o, part_ml = 1, 0, None, None
+            if ctx.decode_only:
+                # a request alone is one CTA per 64 (token, head) rows: its key blocks are dealt to as many CTAs as fill
+                # the SMs twice, no split shorter than 256 keys; a recorded step is sized for its bucket of contexts
+                longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
+                blocks = -(-max(1, longest) // ops.LATENT_KEY_BLOCK)
+                ctas = ctx.n_seqs * -(-self.heads // 64)
+                splits = max(1, min(2 * fast_linear.SMS // ctas, blocks // 8))
+                per_split = -(-blocks // splits)
+                splits = -(-blocks // per_split)
+                if splits > 1:
+                    part_o = ctx.buf((splits, ctx.n_tokens * self.heads, self.kv_rank), torch.float32)
+                    part_ml = ctx.buf((splits, ctx.n_tokens * self.heads, 2), torch.float32)
             ops.latent_attention_bf16(o_lat, qa, cache.k, self.sink, ctx.q_start, ctx.kv_len, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
-                                      self.heads, self.kv_rank, self.rot, self.window, self.scale)
+                                      self.heads, self.kv_rank, self.rot, self.window, self.scale, splits, per_split, part_o, part_ml)
             return
         ops.latent_attention(o_lat, qa, cache.k, self.sink, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
                              self.heads, self.kv_rank, self.rot, self.window, self.scale)

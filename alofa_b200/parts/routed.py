@@ -81,11 +81,9 @@ class RoutedExperts(Part):
     def forward(self, ctx, x, h, store=False):
         n, dt, top, tile = x.shape[0], self.rt.dtype, self.top, ops.MOE_TILE
         i32, f32 = torch.int32, torch.float32
-        z = ctx.buf((n, self.router.shape[0]), f32)
-        ops.gemm_generic(z, x, self.router, None, ops.EPI_STORE)
         choice, weight = ctx.buf((n, top), i32), ctx.buf((n, top), f32)
         gate = ctx.buf((n,), f32) if self.shared_gate else None
-        ops.moe_route(choice, weight, gate, z, self.experts, top, self.score == "softmax", self.renormalize)
+        ops.moe_router(choice, weight, gate, x, self.router, self.experts, top, self.score == "softmax", self.renormalize)
         pairs = n * top
         tiles = -(-pairs // tile) + self.experts  # every expert may end on a tile that is not full
         dest, tile_expert = ctx.buf((n, top), i32), ctx.buf((tiles,), i32)

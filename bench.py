@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--shape 0.5b|1.5b|7b] [--no-extra]
+    python bench.py --design kotutar [--size 1k|2k]     (another line: that design beside Qwen2 at equal layer sizes)
 
 The default run has the layer sizes of the Qwen2.5-0.5B shape with random
 weights, a batch of 8 requests with 2,048-token prompts inside a 4,096-token
@@ -257,7 +258,7 @@ class Bench:
             toks = self.prompt(prompt_len)
             for lo in range(0, prompt_len, PROMPT_LEN):
                 runner.forward_logits([StepEntry(s, toks[lo : lo + PROMPT_LEN], ())])
-        feed = self.rng.integers(0, self.cfg.vocab_size, size=(steps + warmup, batch))
+        feed = self.rng.integers(0, self.runner.model.spec.vocab_size, size=(steps + warmup, batch))
         state = {"i": 0}
 
         def one_step():
@@ -450,6 +451,231 @@ def run(args) -> dict:
     return result
 
 
+# ---------------------------------------------------------------------------------------------------
+# --design kotutar: the latent-attention design beside the Qwen2 design at equal layer sizes
+# ---------------------------------------------------------------------------------------------------
+# Layer sizes after published latent-attention models with routed feed-forwards (random weights):
+# width, heads, unrotated / rotated / value size per head, latent ranks, dense and expert widths.
+DESIGN_SIZES = {
+    "1k": dict(width=1024, heads=8, dim=64, rot=32, vdim=64, kv_rank=256, q_rank=512, ff=4096, experts=16, top=2, expert_ff=512, shared_ff=1024, vocab=32000, layers=4),
+    "2k": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, ff=8192, experts=64, top=6, expert_ff=1408, shared_ff=2816, vocab=32000, layers=4),
+}
+
+
+def kotutar_config(z: dict):
+    """Half of the layers dense, half routed, no loop: what a step costs per layer is what is measured."""
+    from alofa_b200.models.kotutar import KotutarConfig, KotutarLayer, LatentMixerConfig, MlpConfig
+
+    mixer = LatentMixerConfig(z["heads"], z["dim"], z["rot"], z["vdim"], z["kv_rank"], z["q_rank"], (z["dim"] + z["rot"]) ** -0.5, 1e4, z["rot"])
+    layers = [KotutarLayer("latent_attention", mixer, MlpConfig("dense", z["ff"]) if i % 2 == 0 else MlpConfig("moe", z["expert_ff"], z["experts"], z["top"], z["shared_ff"]))
+              for i in range(z["layers"])]
+    return KotutarConfig(z["vocab"], z["width"], 1e-6, layers)
+
+
+def qwen2_config_like(z: dict):
+    """The closest existing design at equal size: same width, layers, heads, head size, vocabulary and feed-forward width; 2 KV heads."""
+    from alofa_b200.models.qwen2 import Qwen2Config
+
+    return Qwen2Config(num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"], num_key_value_heads=2, head_dim=z["width"] // z["heads"],
+                       intermediate_size=z["ff"], vocab_size=z["vocab"], rms_norm_eps=1e-6, rope_theta=1e4, tie_word_embeddings=False, max_position_embeddings=32768)
+
+
+class KernelClock:
+    """Times every kernel call of the package's ops module with its own pair of CUDA events during one
+    step (run outright, no graph), and sets each beside the time its own operands allow: the larger of
+    flops over the measured matrix rate and bytes over the measured copy bandwidth."""
+
+    PRODUCTS = ("gemm_tc", "gemm_generic", "gemm_batched", "gemm_tc_rope")
+    ATTENTION = ("attention_bf16", "latent_attention_bf16", "latent_attention", "paged_attention_generic")
+
+    def __init__(self, peaks: dict):
+        self.peaks = peaks
+        self.calls = []
+
+    @staticmethod
+    def _bytes(args, kwargs) -> int:
+        import torch
+
+        return sum(a.numel() * a.element_size() for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor))
+
+    def ideal_us(self, name, args, kwargs, kv_rows: int) -> tuple:
+        import torch
+
+        byts, flops = self._bytes(args, kwargs), 0.0
+        if name in ("gemm_tc", "gemm_generic"):
+            out, x, w = args[0], args[1], args[2]
+            flops = 2.0 * out.shape[0] * w.shape[0] * w.shape[1]
+        elif name == "gemm_batched":
+            out, x, w, batches, m, n, k = args[:7]
+            by_tile = kwargs.get("tile_batch") is not None
+            flops = 2.0 * m * n * k * (1 if by_tile else batches)
+            byts = (out.element_size() * m * n + x.element_size() * m * k) * (1 if by_tile else batches) + w.numel() * w.element_size()
+        elif name in self.ATTENTION:
+            # out, q, cache(s): every visible row of the cache is read once per request (bytes) and multiplied by every query row (flops)
+            out, q = args[0], args[1]
+            caches = [a for a in args[2:4] if isinstance(a, torch.Tensor) and a.dim() >= 2 and a.dtype == q.dtype]
+            row_bytes = sum(c[0].numel() * c.element_size() for c in caches)
+            byts = out.numel() * out.element_size() + q.numel() * q.element_size() + kv_rows * row_bytes
+            flops = 2.0 * self.pairs * (q.shape[1] + out.shape[1])  # per (query token, key) pair: heads * (score width + value width) multiply-adds
+        ideal = max(flops / (self.peaks["bf16_tflops"] * 1e12), byts / (self.peaks["hbm_gbs"] * 1e9)) * 1e6
+        return ideal, flops, byts
+
+    def run(self, step, kv_rows: int, pairs: float) -> list:
+        """``step()`` runs one step; ``kv_rows``: cache rows the step's requests hold; ``pairs``: (query token, visible key) pairs."""
+        import torch
+
+        from alofa_b200.csrc import ops
+
+        self.pairs = pairs
+        names = [n for n in dir(ops) if not n.startswith("_") and callable(getattr(ops, n)) and getattr(getattr(ops, n), "__module__", "") == ops.__name__
+                 and n not in ("launch_count", "count_launches", "bound_stream", "attention_decode_wide_warps", "attention_decode_slots", "attention_bf16_supported",
+                               "gemm_tc_rope_splits", "gemm_tc_splits", "latent_attention_bf16_supported", "load_library")]
+        originals = {n: getattr(ops, n) for n in names}
+        records = []
+
+        def wrap(name, fn):
+            def timed(*args, **kwargs):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                result = fn(*args, **kwargs)
+                b.record()
+                records.append((name, a, b, self.ideal_us(name, args, kwargs, kv_rows)))
+                return result
+            return timed
+
+        for n, fn in originals.items():
+            setattr(ops, n, wrap(n, fn))
+        try:
+            step()
+            torch.cuda.synchronize()
+        finally:
+            for n, fn in originals.items():
+                setattr(ops, n, fn)
+        table = {}
+        for name, a, b, (ideal, flops, byts) in records:
+            us = a.elapsed_time(b) * 1e3
+            row = table.setdefault(name, {"kernel": name, "calls": 0, "us": 0.0, "ideal_us": 0.0})
+            row["calls"] += 1
+            row["us"] += us
+            row["ideal_us"] += ideal
+        out = sorted(table.values(), key=lambda r: -r["us"])
+        for r in out:
+            r["of_roofline"] = round(r["ideal_us"] / r["us"], 4) if r["us"] > 0 else None
+            r["us"], r["ideal_us"] = round(r["us"], 1), round(r["ideal_us"], 1)
+        return out
+
+
+class DesignBench(Bench):
+    """One engine of one design at one size, measured like the headline bench's."""
+
+    def __init__(self, architecture: str, cfg, label: str, vocab: int, weight_bytes: int, kv_bytes_per_token: int, flops_per_token: float, attn_flops_per_pair: float, max_batch: int):
+        import numpy as np
+
+        from alofa_b200.engine.engine import Engine
+
+        self.label, self.cfg = label, cfg
+        self.vocab = vocab
+        self.engine = Engine.from_random(architecture, cfg, seed=0, dtype="bfloat16", generate_on_device=True, block_size=64, max_batch=max_batch,
+                                         max_tokens=CONTEXT, token_budget=PROMPT_LEN + max_batch, max_chunk=PROMPT_LEN)
+        self.runner = self.engine.runner
+        self.numbers = {"weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token}
+        self.flops_per_token, self.attn_flops_per_pair = flops_per_token, attn_flops_per_pair
+        self.peaks, self.peaks_kind = peaks()
+        self.rng = np.random.default_rng(0)
+
+    def prompt(self, n: int) -> list:
+        return [int(t) for t in self.rng.integers(0, self.vocab, size=n)]
+
+    def prefill(self, warmup: int, reps: int = 10) -> dict:
+        from alofa_b200.engine.step import StepEntry
+
+        tokens = self.prompt(PROMPT_LEN)
+
+        def one():
+            slot = self.runner.admit(10_000)
+            self.runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))])
+            self.runner.release(slot)
+
+        for _ in range(max(3, warmup)):
+            one()
+        _, each = self.timed_each(one, reps)
+        ms = statistics.median(each)
+        flops = self.flops_per_token * PROMPT_LEN + self.attn_flops_per_pair * PROMPT_LEN * (PROMPT_LEN + 1) / 2
+        return {"tok_s": round(PROMPT_LEN / ms * 1e3, 1), "ms": round(ms, 4), "flops_frac": round(flops / (ms * 1e-3) / (self.peaks["bf16_tflops"] * 1e12), 4)}
+
+    def kernels(self, batch: int) -> dict:
+        """Per-kernel times of one prefill step and one decode step of ``batch`` requests, run outright."""
+        from alofa_b200.engine.step import StepEntry
+
+        clock = KernelClock(self.peaks)
+        runner = self.runner
+        graphs, runner.cuda_graphs, runner.prompt_graphs = (runner.cuda_graphs, runner.prompt_graphs), False, False
+        try:
+            tokens = self.prompt(PROMPT_LEN)
+            slot = runner.admit(30_000)
+            runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))])  # loads every kernel
+            runner.release(slot)
+            slot = runner.admit(30_001)
+            prefill = clock.run(lambda: runner.forward_logits([StepEntry(slot, tokens, (PROMPT_LEN - 1,))]), PROMPT_LEN, PROMPT_LEN * (PROMPT_LEN + 1) / 2)
+            runner.release(slot)
+            slots = [runner.admit(31_000 + i) for i in range(batch)]
+            for s_ in slots:
+                runner.forward_logits([StepEntry(s_, self.prompt(PROMPT_LEN), ())])
+            one = lambda: runner.forward_logits([StepEntry(s_, (1,), (0,)) for s_ in slots])
+            one()
+            decode = clock.run(one, batch * (PROMPT_LEN + 2), batch * (PROMPT_LEN + 2))
+            for s_ in slots:
+                runner.release(s_)
+        finally:
+            runner.cuda_graphs, runner.prompt_graphs = graphs
+        return {"prefill_2048": prefill[:8], f"decode_b{batch}": decode[:8]}
+
+
+def design_numbers(design: str, z: dict) -> dict:
+    """Bytes a decode step reads and flops a token costs, from the sizes (bf16)."""
+    w, h = z["width"], z["heads"]
+    if design == "kotutar":
+        d_row = z["kv_rank"] + z["rot"]
+        mixer = w * (z["q_rank"] + d_row) + z["q_rank"] * h * (z["dim"] + z["rot"]) + h * z["dim"] * z["kv_rank"] + h * z["vdim"] * z["kv_rank"] + h * z["vdim"] * w
+        dense = 2 * w * z["ff"]
+        expert = 2 * w * z["expert_ff"]
+        shared = 2 * w * z["shared_ff"]
+        n_dense, n_moe = (z["layers"] + 1) // 2, z["layers"] // 2
+        params_all = z["layers"] * mixer + n_dense * dense + n_moe * (z["experts"] * expert + shared + (z["experts"] + 1) * w)
+        per_token = z["layers"] * mixer + n_dense * dense + n_moe * (z["top"] * expert + shared + (z["experts"] + 1) * w)
+        return {"weight_bytes": 2 * (params_all + z["vocab"] * w), "kv_bytes_per_token": z["layers"] * d_row * 2, "flops_per_token": 2.0 * per_token,
+                "attn_flops_per_pair": z["layers"] * 2.0 * h * (d_row + z["kv_rank"]), "head_flops": 2.0 * w * z["vocab"]}
+    hd, kv = w // h, 2 * (w // h)
+    per_layer = w * (h * hd + 2 * kv) + h * hd * w + 3 * w * z["ff"]
+    return {"weight_bytes": 2 * (z["layers"] * per_layer + 2 * z["vocab"] * w), "kv_bytes_per_token": z["layers"] * 2 * kv * 2, "flops_per_token": 2.0 * z["layers"] * per_layer,
+            "attn_flops_per_pair": z["layers"] * 4.0 * h * hd, "head_flops": 2.0 * w * z["vocab"]}
+
+
+def run_designs(args) -> dict:
+    """Prefill and decode of the latent-attention design beside the Qwen2 design at equal layer sizes,
+    and the kernels of one step of each against their own rooflines."""
+    from alofa_b200.models import kotutar, qwen2
+
+    out = {"metric": "prefill and decode of the Kotutar design beside Qwen2 at equal layer sizes", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+           "prompt_tokens": PROMPT_LEN, "context": CONTEXT, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+    for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
+        z = DESIGN_SIZES[size]
+        row = {"sizes": z}
+        for design, name, cfg in (("kotutar", kotutar.NAME, kotutar_config(z)), ("qwen2", qwen2.NAME, qwen2_config_like(z))):
+            n = design_numbers(design, z)
+            bench = DesignBench(name, cfg, f"{design} {size}", z["vocab"], n["weight_bytes"], n["kv_bytes_per_token"], n["flops_per_token"], n["attn_flops_per_pair"], 64)
+            res = {"prefill_2048": bench.prefill(args.warmup)}
+            for batch in (8, 64):
+                point = bench.decode(batch, min(args.steps, 64), args.warmup)
+                res[f"decode_b{batch}"] = {"tok_s": round(point["tok_s"], 1), "ms_per_step": round(point["ms"], 4), "hbm_frac": round(point["frac"], 4), "launches_per_step": point["launches"] // max(1, min(args.steps, 64))}
+            res["kernels"] = bench.kernels(64)
+            res["peaks"] = bench.peaks_kind
+            row[design] = res
+            bench.close()
+        out["sizes"][size] = row
+    return out
+
+
 def reference_arm() -> dict:
     """The reference is a Mojo project: it has no Python package to install and
     neither `mojo` nor `pixi` exists in this image, so it cannot run here."""
@@ -467,6 +693,8 @@ def main() -> int:
     ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="whose layer sizes the headline run has")
     ap.add_argument("--no-extra", dest="extra", action="store_false", help="leave out the measurements beside the headline (long contexts, the 1.5B and 7B shapes)")
+    ap.add_argument("--design", choices=["kotutar"], help="instead of the headline run: this design beside Qwen2 at equal layer sizes (prefill, decode, kernels against their rooflines)")
+    ap.add_argument("--size", choices=sorted(DESIGN_SIZES), help="with --design: one of the sizes only")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps(reference_arm()))
@@ -475,6 +703,9 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        print(json.dumps(run_designs(args)))
+        return 0
     print(json.dumps(run(args)))
     return 0
 

@@ -137,15 +137,21 @@ def test_latent_attention_over_paged_rows(dtype, heads, kv_rank, rot, window):
             at += len(p)
 
 
-def run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv_rank, rot, scale, window=None, page=16):
-    """The tensor-core kernel on the last ``portions[r]`` tokens of every request, all in one launch."""
+def run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv_rank, rot, scale, window=None, page=16, splits=1):
+    """The tensor-core kernel on the last ``portions[r]`` tokens of every request, all in one launch;
+    ``splits`` > 1: every request's key blocks dealt to that many CTAs and merged."""
     from alofa_b200.csrc import ops
 
+    per_split, part_o, part_ml = 0, None, None
+    if splits > 1:
+        per_split = -(-(-(-max(lengths) // ops.LATENT_KEY_BLOCK)) // splits)
+        part_o = torch.full((splits, sum(portions) * heads, kv_rank), 7.0, dtype=F32, device="cuda")
+        part_ml = torch.full((splits, sum(portions) * heads, 2), 7.0, dtype=F32, device="cuda")
     q = np.concatenate([qa[r][n - k : n] for r, (n, k) in enumerate(zip(lengths, portions))]).reshape(-1, heads * (kv_rank + rot))
     q_start = np.concatenate([[0], np.cumsum(portions)]).astype(np.int32)
     out = torch.empty((len(q), heads * kv_rank), dtype=BF16, device="cuda")
     ops.latent_attention_bf16(out, dev(q, BF16), cache, dev(sink, F32) if sink is not None else None, dev(q_start), dev(np.array(lengths, dtype=np.int32)), table, page,
-                              len(lengths), max(portions), heads, kv_rank, rot, window, scale)
+                              len(lengths), max(portions), heads, kv_rank, rot, window, scale, splits, per_split, part_o, part_ml)
     return out.float().cpu().numpy().reshape(-1, heads, kv_rank), q_start
 
 
@@ -166,6 +172,10 @@ def test_latent_attention_on_tensor_cores(heads, kv_rank, rot, window, sunk):
         got, q_start = run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv_rank, rot, 1.3, window)
         for r, (n, k) in enumerate(zip(lengths, portions)):
             assert_close(got[q_start[r] : q_start[r + 1]], want[r][n - k : n], KERNEL_TOL[BF16], f"{what}: request {r} ({n} rows, last {k})")
+    for splits in (2, 3, 5):  # decoding with the keys dealt to several CTAs: shares that are empty, one block, several
+        got, q_start = run_latent_attention_tc(qa, cache, table, sink, lengths, [1] * len(lengths), heads, kv_rank, rot, 1.3, window, splits=splits)
+        for r, n in enumerate(lengths):
+            assert_close(got[r], want[r][n - 1], KERNEL_TOL[BF16], f"{splits} splits: request {r} ({n} rows)")
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -238,6 +248,15 @@ def test_router_sort_scatter_and_combine(experts, top):
     assert (choice.cpu().numpy() == want_choice).all()
     assert_close(weight.cpu(), want_weight, 1e-6, "weights")
     assert_close(gate.cpu(), 1 / (1 + np.exp(-(x @ wr[experts]))), 1e-6, "shared gate")
+    for dtype in (F32, BF16):  # the product and the choice in one kernel
+        c2, w2, g2 = torch.empty_like(choice), torch.empty_like(weight), torch.empty_like(gate)
+        xr = rounded(x, dtype)
+        ops.moe_router(c2, w2, g2, dev(xr, dtype), dev(wr, F32), experts, top)
+        ref_choice, ref_weight = plain.router(xr, {"router": wr[:experts]}, "", top)
+        sure = plain.router_margin(xr, {"router": wr[:experts]}, "", top) > 1e-4
+        assert (c2.cpu().numpy()[sure] == ref_choice[sure]).all() and sure.sum() > n // 2
+        assert_close(w2.cpu().numpy()[sure], ref_weight[sure], 1e-5, "weights of the fused router")
+        assert_close(g2.cpu(), 1 / (1 + np.exp(-(xr @ wr[experts]))), 1e-5, "gate of the fused router")
     tiles = -(-n * top // tile) + experts
     dest, tile_expert = torch.empty((n, top), dtype=torch.int32, device="cuda"), torch.empty((tiles,), dtype=torch.int32, device="cuda")
     ops.moe_sort(dest, tile_expert, choice, experts, tile)
@@ -249,6 +268,14 @@ def test_router_sort_scatter_and_combine(experts, top):
     xs = torch.zeros((tiles * tile, hidden), dtype=F32, device="cuda")
     ops.moe_scatter(xs, dev(x, F32), weight, dest, top)
     assert_close(xs.cpu().numpy()[d], (x[:, None, :] * want_weight[:, :, None]).reshape(n * top, hidden), 1e-6, "scattered rows")
+    many = rng.integers(0, experts, size=(3000, top)).astype(np.int32)  # thousands of pairs: every thread of the sort has a share
+    many_tiles = -(-many.size // tile) + experts
+    d2, te2 = torch.empty(many.shape, dtype=torch.int32, device="cuda"), torch.empty((many_tiles,), dtype=torch.int32, device="cuda")
+    ops.moe_sort(d2, te2, dev(many), experts, tile)
+    d2, te2 = d2.cpu().numpy().ravel(), te2.cpu().numpy()
+    assert len(set(d2.tolist())) == many.size and (te2[d2 // tile] == many.ravel()).all()
+    for e in range(experts):  # within an expert the rows keep the order of the pairs
+        assert (np.diff(d2[many.ravel() == e]) == 1).all()
     y = torch.empty((n, hidden), dtype=F32, device="cuda")
     shared = rounded(rng.standard_normal((n, hidden)), F32)
     ops.moe_combine(y, xs, dest, None, dev(shared, F32), gate, top)
