@@ -581,78 +581,118 @@ __global__ void moe_route_kernel(int* __restrict__ choice, float* __restrict__ w
 }
 
 // The router's product and the choice in one kernel: z = x Wr^T in fp32 (x in the compute dtype, Wr fp32
-// [E (+1), hidden]), one warp per token: every lane sums its share of the depth for one expert at a
-// time, the warp adds the shares in butterfly order (the order depends on the sizes alone), the logits
-// stay in shared memory for the choice above.
-template <typename T>
+// [E (+1), hidden]).  A block takes up to eight tokens, whose rows it keeps in shared memory; a warp takes
+// the experts warp, warp + 8, ... and, for each, sums all the block's tokens at once: every lane reads its
+// share of the expert's weights once and multiplies it into each token's row, then the warp adds the
+// lanes' shares in butterfly order.  The order of additions of a (token, expert) sum depends on the depth
+// alone.  The logits stay in shared memory; then a warp per token takes scores and choice as above.
+template <typename T, int TT>
 __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate,
                                                          const T* __restrict__ x, const float* __restrict__ wr, int T_, int E, int top, int hidden,
                                                          int gated, int softmax, int renormalize) {
-  extern __shared__ float sc[];  // [8 warps][E + 1]
+  extern __shared__ __align__(16) uint8_t router_smem[];
+  const int cols = E + (gated ? 1 : 0);
+  float* z = reinterpret_cast<float*>(router_smem);      // [TT][cols]
+  T* xs = reinterpret_cast<T*>(z + TT * cols + ((TT * cols) & 1));  // [TT][hidden]
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 8 + warp;
-  if (t >= T_) return;
-  float* s = sc + warp * (E + 1);
-  const T* xr = x + (size_t)t * hidden;
-  const int cols = E + (gated ? 1 : 0);
-  for (int e = 0; e < cols; ++e) {
+  const int t0 = blockIdx.x * TT;
+  const int live = min(TT, T_ - t0);
+  for (int e = threadIdx.x; e < TT * hidden; e += 256) {
+    const int r = e / hidden;
+    xs[e] = r < live ? x[(size_t)t0 * hidden + e] : from_f<T>(0.f);
+  }
+  __syncthreads();
+  for (int e = warp; e < cols; e += 8) {
     const float* w = wr + (size_t)e * hidden;
-    float dot = 0.f;
-    for (int c = lane; c < hidden; c += 32) dot = fmaf(to_f(xr[c]), w[c], dot);
-    dot = warp_sum(dot);
-    if (lane == 0) s[e] = dot;
-  }
-  __syncwarp();
-  const float zg = gated ? s[E] : 0.f;
-  if (softmax) {
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-      s[e] = expf(s[e] - mx);
-      sum += s[e];
-    }
-    sum = warp_sum(sum);
-    for (int e = lane; e < E; e += 32) s[e] /= sum;
-  } else {
-    for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
-  }
-  __syncwarp();
-  float total = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int arg = 0x7fffffff;
-    for (int e = lane; e < E; e += 32)
-      if (s[e] > best) best = s[e], arg = e;
+    float dot[TT];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-      if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+    for (int r = 0; r < TT; ++r) dot[r] = 0.f;
+    for (int c = lane; c < hidden; c += 32) {
+      const float wv = w[c];
+#pragma unroll
+      for (int r = 0; r < TT; ++r) dot[r] = fmaf(to_f(xs[r * hidden + c]), wv, dot[r]);
     }
-    if (arg >= E) arg = k, best = 0.f;
-    if (lane == 0) {
-      choice[(size_t)t * top + k] = arg;
-      weight[(size_t)t * top + k] = best;
-      s[arg] = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < TT; ++r) {
+      const float v = warp_sum(dot[r]);
+      if (lane == 0) z[r * cols + e] = v;
     }
-    total += best;
-    __syncwarp();
   }
-  if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
-  if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zg));
+  __syncthreads();
+  for (int r = warp; r < live; r += 8) {
+    const int t = t0 + r;
+    float* s = z + r * cols;
+    const float zg = gated ? s[E] : 0.f;
+    if (softmax) {
+      float mx = -INFINITY;
+      for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s[e]);
+      mx = warp_max(mx);
+      float sum = 0.f;
+      for (int e = lane; e < E; e += 32) {
+        s[e] = expf(s[e] - mx);
+        sum += s[e];
+      }
+      sum = warp_sum(sum);
+      for (int e = lane; e < E; e += 32) s[e] /= sum;
+    } else {
+      for (int e = lane; e < E; e += 32) s[e] = 1.0f / (1.0f + expf(-s[e]));
+    }
+    __syncwarp();
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      for (int e = lane; e < E; e += 32)
+        if (s[e] > best) best = s[e], arg = e;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+      }
+      if (arg >= E) arg = k, best = 0.f;
+      if (lane == 0) {
+        choice[(size_t)t * top + k] = arg;
+        weight[(size_t)t * top + k] = best;
+        s[arg] = -INFINITY;
+      }
+      total += best;
+      __syncwarp();
+    }
+    if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+    if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zg));
+  }
+}
+
+template <typename T, int TT>
+static int moe_router_launch(int* choice, float* weight, float* gate, const void* x, const float* wr, int T_, int E, int top, int hidden, int softmax,
+                             int renormalize, cudaStream_t stream) {
+  const int cols = E + (gate ? 1 : 0);
+  const size_t smem = ((size_t)TT * cols + 1) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
+  static size_t set = 0;
+  if (smem > set) {
+    if (cudaFuncSetAttribute(moe_router_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    set = smem;
+  }
+  launch_dep(moe_router_kernel<T, TT>, (T_ + TT - 1) / TT, 256, smem, stream, choice, weight, gate, (const T*)x, wr, T_, E, top, hidden, gate ? 1 : 0, softmax,
+             renormalize);
+  return launch_status();
 }
 
 ALOFA_API int alofa_moe_router(int* choice, float* weight, float* gate, const void* x, const float* wr, int T, int E, int top, int hidden, int softmax,
                                int renormalize, int x_bf16, cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
-  if (E <= 0 || top <= 0 || top > E || top > 32 || (size_t)8 * (E + 1) * 4 > 48 * 1024) return ALOFA_ERR_ARGUMENT;
-  const size_t smem = (size_t)8 * (E + 1) * sizeof(float);
-  if (x_bf16) launch_dep(moe_router_kernel<bf16>, (T + 7) / 8, 256, smem, stream, choice, weight, gate, (const bf16*)x, wr, T, E, top, hidden, gate ? 1 : 0, softmax, renormalize);
-  else launch_dep(moe_router_kernel<float>, (T + 7) / 8, 256, smem, stream, choice, weight, gate, (const float*)x, wr, T, E, top, hidden, gate ? 1 : 0, softmax, renormalize);
-  return launch_status();
+  if (E <= 0 || top <= 0 || top > E || top > 32) return ALOFA_ERR_ARGUMENT;
+  const size_t row = (size_t)hidden * (x_bf16 ? 2 : 4) + (size_t)(E + 1) * 4;
+  const size_t room = 200 * 1024;
+  if (8 * row <= room)
+    return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream)
+                  : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream);
+  if (2 * row <= room)
+    return x_bf16 ? moe_router_launch<bf16, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream)
+                  : moe_router_launch<float, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream);
+  return ALOFA_ERR_ARGUMENT;
 }
 
 ALOFA_API int alofa_moe_route(int* choice, float* weight, float* gate, const float* z, int T, int E, int top, int cols, int softmax, int renormalize,

@@ -6,7 +6,7 @@
 // portion is (token r / heads, head r % heads), and a CTA owns 64 consecutive
 // rows, which lie contiguously in the absorbed-query matrix qa [T, heads, D].  A
 // decode token alone gives `heads` rows, a prompt portion many tiles.  Keys come
-// in blocks of 32 rows of the paged cache (cp.async, double buffered); the same
+// in blocks of 32 rows of the paged cache (cp.async, a ring of blocks); the same
 // block in shared memory is the key operand (all D columns) and the value
 // operand (its first KV_RANK columns).  Eight warps: warp = (row group of 16
 // rows, half of the value columns).  Both halves of a row group compute the
@@ -37,10 +37,12 @@ namespace {
 
 constexpr int D = KV_RANK + ROT;
 constexpr int PITCH = D + 8;          // elements per row in shared memory: 16 bytes of padding keep ldmatrix off bank conflicts
-constexpr int BM = 64, BN = 32;
-constexpr int STAGES = 3;             // key blocks in flight per CTA
-constexpr int THREADS = 256;
-constexpr int MIN_CTAS = KV_RANK <= 256 ? 2 : 1;  // the output accumulators are KV_RANK / 4 registers a thread
+constexpr int BN = 32;                // keys per block
+// Two shapes of the CTA.  Wide: four row groups (64 rows), eight warps, three key blocks in flight: prompt
+// portions, and decode tokens of more than 16 heads.  Narrow: one row group (16 rows), two warps, two key
+// blocks in flight, two CTAs to an SM: decode tokens of up to 16 heads, whose rows would fill a quarter of
+// the wide tile while its other warps only fetched.
+constexpr int MIN_CTAS_WIDE = KV_RANK <= 256 ? 2 : 1;  // the output accumulators are KV_RANK / 4 registers a thread
 constexpr int HALF = KV_RANK / 2;     // value columns per warp
 constexpr int NT = HALF / 8;          // n-tiles of the output per warp
 static_assert(KV_RANK % 32 == 0 && D % 16 == 0, "latent sizes this kernel takes");
@@ -65,11 +67,13 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-__global__ void __launch_bounds__(THREADS, MIN_CTAS)
+template <int GROUPS, int STAGES>
+__global__ void __launch_bounds__(GROUPS * 64, GROUPS == 1 ? 2 : MIN_CTAS_WIDE)
 latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa, const bf16* __restrict__ cache, const float* __restrict__ sink,
                              const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table, int max_blocks,
                              int page_size, int heads, int window, float scale_log2, float* __restrict__ part_o, float* __restrict__ part_ml,
                              int blocks_per_split, int total_rows) {
+  constexpr int BM = 16 * GROUPS, THREADS = 64 * GROUPS;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][PITCH]
   bf16* Ks = Qs + BM * PITCH;                        // [STAGES][BN][PITCH]
@@ -82,7 +86,7 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
   const int pos0 = n_keys - q_len;           // position of the portion's first token
   const int* table = block_table + (size_t)seq * max_blocks;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rg = warp & 3, ch = warp >> 2, g = lane >> 2, t = lane & 3;
+  const int rg = warp % GROUPS, ch = warp / GROUPS, g = lane >> 2, t = lane & 3;
 
   // the query tile: 64 consecutive rows of qa
   {
@@ -107,18 +111,20 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
     b_hi = min(b_hi, ((int)blockIdx.z + 1) * blocks_per_split - 1);
   }
 
+  // A block's rows are dealt to the threads, THREADS / BN threads to a row: a thread finds its row's slot
+  // once (one division, one block-table entry) and copies every (THREADS / BN)-th 16-byte chunk of the row.
   auto fetch = [&](int b, int buf) {
-    bf16* dst = Ks + (size_t)buf * BN * PITCH;
-    constexpr int CHUNKS = D / 8;
-    for (int e = tid; e < BN * CHUNKS; e += THREADS) {
-      const int j = e / CHUNKS, c = e - j * CHUNKS;
-      const int key = b * BN + j;
-      if (key <= key_hi) {
-        const int slot = table[key / page_size] * page_size + key % page_size;
-        cp16(smem_addr(dst + j * PITCH + c * 8), cache + (size_t)slot * D + c * 8);
-      } else {
-        *reinterpret_cast<uint4*>(dst + j * PITCH + c * 8) = make_uint4(0, 0, 0, 0);
-      }
+    constexpr int CHUNKS = D / 8, PER_ROW = THREADS / BN;
+    const int j = tid / PER_ROW, c0 = tid - j * PER_ROW;
+    bf16* dst = Ks + ((size_t)buf * BN + j) * PITCH;
+    const int key = b * BN + j;
+    if (key <= key_hi) {
+      const int page = key / page_size;
+      const bf16* src = cache + ((size_t)table[page] * page_size + (key - page * page_size)) * D;
+#pragma unroll 4
+      for (int c = c0; c < CHUNKS; c += PER_ROW) cp16(smem_addr(dst + c * 8), src + c * 8);
+    } else {
+      for (int c = c0; c < CHUNKS; c += PER_ROW) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
     }
   };
 #pragma unroll
@@ -154,6 +160,10 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
     cp_wait<STAGES - 1>();
     __syncthreads();
     const bf16* Kb = Ks + (size_t)buf * BN * PITCH;
+    if (r0 + rg * 16 >= rows) {  // a row group without a live row (a decode token's heads fill a part of the tile): it only helps to fetch
+      __syncthreads();
+      continue;
+    }
     // S = Q K^T for 16 rows x 32 keys
     float s[4][4];
 #pragma unroll
@@ -282,17 +292,26 @@ ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void*
   if (heads <= 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
   if (splits < 1) splits = 1;
   if (splits > 1 && (!part_o || !part_ml || blocks_per_split <= 0 || total_rows <= 0 || splits > 65535)) return ALOFA_ERR_ARGUMENT;
-  const size_t smem = (size_t)(BM + STAGES * BN) * PITCH * sizeof(bf16);
+  const bool narrow = (long long)max_q_len * heads <= 16;
+  const int bm = narrow ? 16 : 64, stages = narrow ? 2 : 3;
+  const size_t smem = (size_t)(bm + stages * BN) * PITCH * sizeof(bf16);
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(latent_attention_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(latent_attention_bf16_kernel<4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((64 + 3 * BN) * PITCH * sizeof(bf16))) != cudaSuccess ||
+        cudaFuncSetAttribute(latent_attention_bf16_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((16 + 2 * BN) * PITCH * sizeof(bf16))) != cudaSuccess)
+      return ALOFA_ERR_LAUNCH;
     set = true;
   }
-  const long long tiles = ((long long)max_q_len * heads + BM - 1) / BM;
+  const long long tiles = ((long long)max_q_len * heads + bm - 1) / bm;
   if (tiles > 2147483647LL || n_seqs > 65535) return ALOFA_ERR_ARGUMENT;
-  launch_dep(latent_attention_bf16_kernel, dim3((unsigned)tiles, n_seqs, splits), dim3(THREADS), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache,
-             sink, q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f, part_o, part_ml, blocks_per_split,
-             total_rows);
+  if (narrow)
+    launch_dep(latent_attention_bf16_kernel<1, 2>, dim3((unsigned)tiles, n_seqs, splits), dim3(64), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache,
+               sink, q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f, part_o, part_ml, blocks_per_split,
+               total_rows);
+  else
+    launch_dep(latent_attention_bf16_kernel<4, 3>, dim3((unsigned)tiles, n_seqs, splits), dim3(256), smem, stream, (bf16*)out, (const bf16*)qa, (const bf16*)cache,
+               sink, q_start, kv_len, block_table, max_blocks, page_size, heads, window, scale * 1.4426950408889634f, part_o, part_ml, blocks_per_split,
+               total_rows);
   if (splits > 1) launch_dep(latent_attention_merge_kernel, dim3(total_rows), dim3(128), 0, stream, (bf16*)out, part_o, part_ml, splits, total_rows);
   return launch_status();
 }
@@ -300,5 +319,5 @@ ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void*
 ALOFA_API int alofa_latent_attention_bf16_sizes(int* kv_rank, int* rot) {
   *kv_rank = KV_RANK;
   *rot = ROT;
-  return (int)((BM + STAGES * BN) * PITCH * sizeof(bf16));
+  return (int)((64 + 3 * BN) * PITCH * sizeof(bf16));
 }

@@ -135,12 +135,14 @@ class LatentAttention(Part):
         if qa.dtype == torch.bfloat16 and ops.latent_attention_bf16_supported(self.kv_rank, self.rot):
             splits, per_split, part_o, part_ml = 1, 0, None, None
             if ctx.decode_only:
-                # a request alone is one CTA per 64 (token, head) rows: its key blocks are dealt to as many CTAs as fill
-                # the SMs twice, no split shorter than 256 keys; a recorded step is sized for its bucket of contexts
+                # a request alone is one CTA per 64 (token, head) rows: its key blocks are dealt to as many CTAs as are
+                # resident together (two per SM up to a latent of 256, else one; a second wave doubled the time),
+                # no split shorter than 256 keys; a recorded step is sized for its bucket of contexts
                 longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
                 blocks = -(-max(1, longest) // ops.LATENT_KEY_BLOCK)
-                ctas = ctx.n_seqs * -(-self.heads // 64)
-                splits = max(1, min(2 * fast_linear.SMS // ctas, blocks // 8))
+                narrow = self.heads <= 16  # the kernel's narrow shape: 16-row tiles, two CTAs to an SM whatever the latent
+                ctas = ctx.n_seqs * -(-self.heads // (16 if narrow else 64))
+                splits = max(1, min((2 if narrow or self.kv_rank <= 256 else 1) * fast_linear.SMS // ctas, blocks // 8))
                 per_split = -(-blocks // splits)
                 splits = -(-blocks // per_split)
                 if splits > 1:
