@@ -598,20 +598,32 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TT;
   const int live = min(TT, T_ - t0);
-  for (int e = threadIdx.x; e < TT * hidden; e += 256) {
-    const int r = e / hidden;
-    xs[e] = r < live ? x[(size_t)t0 * hidden + e] : from_f<T>(0.f);
-  }
+  for (int r = 0; r < TT; ++r)
+    for (int c = threadIdx.x; c < hidden; c += 256) xs[r * hidden + c] = r < live ? x[(size_t)(t0 + r) * hidden + c] : from_f<T>(0.f);
   __syncthreads();
   for (int e = warp; e < cols; e += 8) {
     const float* w = wr + (size_t)e * hidden;
     float dot[TT];
 #pragma unroll
     for (int r = 0; r < TT; ++r) dot[r] = 0.f;
-    for (int c = lane; c < hidden; c += 32) {
-      const float wv = w[c];
+    if ((hidden & 3) == 0) {
+      // four depth entries a lane and several loads in flight: with one scalar load at a time a warp spent
+      // its time waiting for the weights (190 us a call at 64 experts, whatever the number of tokens)
+#pragma unroll 4
+      for (int c = lane * 4; c < hidden; c += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + c);
 #pragma unroll
-      for (int r = 0; r < TT; ++r) dot[r] = fmaf(to_f(xs[r * hidden + c]), wv, dot[r]);
+        for (int r = 0; r < TT; ++r) {
+          const T* xr = xs + r * hidden + c;
+          dot[r] = fmaf(to_f(xr[3]), wv.w, fmaf(to_f(xr[2]), wv.z, fmaf(to_f(xr[1]), wv.y, fmaf(to_f(xr[0]), wv.x, dot[r]))));
+        }
+      }
+    } else {
+      for (int c = lane; c < hidden; c += 32) {
+        const float wv = w[c];
+#pragma unroll
+        for (int r = 0; r < TT; ++r) dot[r] = fmaf(to_f(xs[r * hidden + c]), wv, dot[r]);
+      }
     }
 #pragma unroll
     for (int r = 0; r < TT; ++r) {
