@@ -29,13 +29,13 @@ template <typename TO>
 __global__ void __launch_bounds__(128) gemm_batched_bf16_kernel(TO* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                                 const float* __restrict__ bias, const int* __restrict__ tile_batch, int M, int N,
                                                                 int K, long long ldx, long long x_batch, long long ldw, long long w_batch,
-                                                                long long ldo, long long out_batch, long long bias_batch, int act) {
+                                                                long long ldo, long long out_batch, long long bias_batch, int act, int tile_rows) {
   __shared__ __align__(16) bf16 As[2][TM * LD];
   __shared__ __align__(16) bf16 Bs[2][TN * LD];
   pdl_begin();
   int b = blockIdx.z;
   if (tile_batch) {
-    b = tile_batch[blockIdx.y];
+    b = tile_batch[blockIdx.y * 64 / tile_rows];  // tile_rows is a multiple of this kernel's 64 rows
     if (b < 0) return;
   } else {
     x += (size_t)b * x_batch;
@@ -109,16 +109,17 @@ __global__ void __launch_bounds__(128) gemm_batched_bf16_kernel(TO* __restrict__
 
 ALOFA_API int alofa_gemm_batched_bf16(void* out, const void* x, const void* w, const float* bias, const int* tile_batch, int batches, int M, int N, int K,
                                       long long ldx, long long x_batch, long long ldw, long long w_batch, long long ldo, long long out_batch,
-                                      long long bias_batch, int act, int out_bf16, cudaStream_t stream) {
+                                      long long bias_batch, int act, int tile_rows, int out_bf16, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || batches <= 0) return ALOFA_OK;
+  if (tile_batch && (tile_rows <= 0 || tile_rows % TM)) return ALOFA_ERR_ARGUMENT;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || (x_batch & 7) || (w_batch & 7) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ALOFA_ERR_ARGUMENT;
   if ((M + TM - 1) / TM > 65535 || batches > 65535) return ALOFA_ERR_ARGUMENT;
   dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, tile_batch ? 1 : batches);
   if (out_bf16)
     launch_dep(gemm_batched_bf16_kernel<bf16>, grid, dim3(128), 0, stream, (bf16*)out, (const bf16*)x, (const bf16*)w, bias, tile_batch, M, N, K, ldx, x_batch,
-               ldw, w_batch, ldo, out_batch, bias_batch, act);
+               ldw, w_batch, ldo, out_batch, bias_batch, act, tile_rows);
   else
     launch_dep(gemm_batched_bf16_kernel<float>, grid, dim3(128), 0, stream, (float*)out, (const bf16*)x, (const bf16*)w, bias, tile_batch, M, N, K, ldx,
-               x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act);
+               x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act, tile_rows);
   return launch_status();
 }

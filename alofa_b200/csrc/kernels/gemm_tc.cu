@@ -64,6 +64,10 @@ struct GemmArgs {
   int k_slices_per_split;
   int out_bf16;
   int act;            // EPI_STORE: an activation on the sums plus bias (codes of common.cuh), 0 for none
+  // Tokens on M, EPI_STORE, by tile: the weight is [batches * N, K] and the token tile i (128 rows)
+  // multiplies by the rows of batch tile_batch[i], negative: the tile is empty (the experts of a routed
+  // feed-forward, rows sorted by expert and padded to whole tiles; the array is written on the device)
+  const int* tile_batch;
   int pair;           // tokens on M: the wide product runs on pairs of CTAs (the weight map's box is then 128 rows)
   int few;            // tokens on M, persistent, up to 64 tokens: the token map's box is this many rows (32 or 64), else 0
   int* status;
@@ -780,7 +784,9 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int f0 = blockIdx.x * FEATS, t0 = blockIdx.y * 128;
   const int total_slices = (args.K + BK - 1) / BK;
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
-  const int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
+  int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
+  int w_row = f0;       // the first weight row of this tile (by tile: inside the tile's batch)
+  bool no_tile = false; // by tile: this token tile names no batch, nothing is computed or stored
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -805,18 +811,30 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
       tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, args.N + f0);
     } else {
-      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, w_row);
     }
   };
   // the weights depend on no earlier kernel: the first ring of them is asked for ahead of the wait
+  // (not by tile: which weights a tile takes is what an earlier kernel of the step decided)
   int early_slices = 0;
   if (threadIdx.x == 0) {
     asm volatile("griddepcontrol.launch_dependents;");
-    early_slices = min(stages, n_slices);
-    for (int i = 0; i < early_slices; ++i) load_weights(i);
+    if (!args.tile_batch) {
+      early_slices = min(stages, n_slices);
+      for (int i = 0; i < early_slices; ++i) load_weights(i);
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
   } else {
     pdl_begin();  // set-up above overlaps the previous kernel; its results are read from here on
+  }
+  if (args.tile_batch) {
+    const int batch = args.tile_batch[blockIdx.y];
+    if (batch < 0) {
+      no_tile = true;
+      n_slices = 0;
+    } else {
+      w_row = batch * args.N + f0;
+    }
   }
 
   if (warp == 0) {
@@ -851,7 +869,9 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     ok = epilogue_warps_agree(ok);  // the quarter's other warp must not be left waiting for this one
     tc_fence_after();
     const bool staged = (args.N & 3) == 0 && !(GATED && gridDim.z > 1);
-    if (ok && staged && t0 + q * 32 < args.T) {
+    if (no_tile) {
+      // nothing to store
+    } else if (ok && staged && t0 + q * 32 < args.T) {
       tokens_epilogue_staged<BNF, EPI>(args, tmem_base, reinterpret_cast<float*>(tiles), q, half, lane, f0, t0, (int)gridDim.z, (int)blockIdx.z, nullptr);
     } else if (ok && t0 + q * 32 < args.T) {
       // widths that are no multiple of 4 (or gated partial sums): element-wise, straight from the registers
@@ -1483,7 +1503,7 @@ static int launch_tokens(const CUtensorMap& mw, const CUtensorMap& mx, const Gem
     prefer_max_shared(gemm_tc_tokens_kernel<BNF, EPI>);
     configured = true;
   }
-  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && (args.K <= 2048 || args.pair)) {
+  if (BNF == 256 && splits == 1 && (args.N & 3) == 0 && (args.K <= 2048 || args.pair) && !args.tile_batch) {
     // More tiles than SMs and a shallow depth, where a tile's epilogue is a large share of its
     // time: one resident CTA per SM works through the tiles, epilogues beside MMAs.  (Deep
     // products measured faster as two CTAs per SM, which keep four stages in flight per SM.)
@@ -1582,12 +1602,15 @@ ALOFA_API int alofa_gemm_tc_reduces_in_cluster(int epi, int bn, int splits) {
 ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float* bias, float* partial, int T, int N, int K, int epi, int out_bf16,
                             int bn, int splits, int do_reduce, int* status, int b_kind, const float* b_src, const float* b_ml,
                             const int* b_positions, int b_heads, int b_head_dim, int b_window, int b_split_keys, long long* acc,
-                            const long long* n_acc, const float* n_gamma, float n_eps, float* n_out, long long* n_zero, cudaStream_t stream) {
+                            const long long* n_acc, const float* n_gamma, float n_eps, float* n_out, long long* n_zero, const int* tile_batch,
+                            int batches, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return ALOFA_OK;
   const int act = epi >> 4;  // EPI_STORE | (code << 4): an activation on the sums plus bias
   epi &= 15;
   if (act && (epi != EPI_STORE || b_kind != B_ROWS)) return ALOFA_ERR_ARGUMENT;
   if (acc && (epi != EPI_RESIDUAL || bn <= 0)) return ALOFA_ERR_ARGUMENT;
+  // by tile: tokens on M, whole tiles of 128 rows, a stored product without bias or depth split
+  if (tile_batch && (bn >= 0 || epi != EPI_STORE || bias || splits > 1 || b_kind != B_ROWS || batches <= 0 || (T & 127))) return ALOFA_ERR_ARGUMENT;
   if (b_kind == B_NORMED) {
     if (bn != 16 || T > 16 || epi != EPI_GATED || !b_src || !n_gamma || !n_out || n_out == b_src || (K % 8) != 0 || !do_reduce) return ALOFA_ERR_ARGUMENT;
     if (((uintptr_t)b_src & 15) || ((uintptr_t)n_gamma & 15) || ((uintptr_t)n_out & 15) || ((uintptr_t)n_acc & 15) || ((uintptr_t)n_zero & 15)) return ALOFA_ERR_ARGUMENT;
@@ -1605,14 +1628,14 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   if (splits < 1) splits = 1;
   if (splits > total_slices) splits = total_slices;
   if (splits > 1 && !partial && !acc && b_kind != B_NORMED) return ALOFA_ERR_ARGUMENT;
-  const int w_rows = (epi == EPI_GATED) ? 2 * N : N;
+  const int w_rows = tile_batch ? batches * N : (epi == EPI_GATED) ? 2 * N : N;
   // bn > 0: weights on the M side, bn tokens per CTA.  bn < 0: tokens on the M
   // side (128 per CTA), -bn weight rows per MMA (for GATED half gate, half up).
   const bool tokens_on_m = bn < 0;
   const int bnf = -bn;
   CUtensorMap mw, mx;
-  const bool pair = tokens_on_m && pair_product(bnf, splits, T, N, K, epi);
-  const int few = (tokens_on_m && !pair) ? few_tokens_product(bnf, splits, T, N, K, epi) : 0;
+  const bool pair = tokens_on_m && !tile_batch && pair_product(bnf, splits, T, N, K, epi);
+  const int few = (tokens_on_m && !pair && !tile_batch) ? few_tokens_product(bnf, splits, T, N, K, epi) : 0;
   if (tokens_on_m) {
     const int w_box = (epi == EPI_GATED || pair) ? bnf / 2 : bnf;
     if (!make_map(&mw, w, w_rows, K, w_box) || !make_map(&mx, x, T, K, few ? few : 128)) return ALOFA_ERR_ARGUMENT;
@@ -1631,6 +1654,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   splits = (total_slices + args.k_slices_per_split - 1) / args.k_slices_per_split;  // no empty split
   args.out_bf16 = out_bf16;
   args.act = act;
+  args.tile_batch = tile_batch;
   args.pair = pair ? 1 : 0;
   args.few = few;
   args.status = status;

@@ -159,7 +159,7 @@ ALOFA_API int alofa_rotary_interleaved(void* x, const float* freq, const int* po
 // Batched product with strides: for batch b, out_b[m, n] = act(sum_k x_b[m, k] * w_b[n, k] + bias_b[n]),
 //   x_b = x + b * x_batch (row stride ldx), w_b = w + b * w_batch (row stride ldw),
 //   out_b = out + b * out_batch (row stride ldo), bias_b = bias + b * bias_batch.
-// With tile_batch (one entry per 64-row tile of M) there is one x and one out,
+// With tile_batch (one entry per tile of tile_rows rows of M, a multiple of 64) there is one x and one out,
 // and tile i multiplies by the weight of batch tile_batch[i] (negative: the
 // tile is empty): rows sorted by expert, each expert's rows padded to whole tiles.
 // 64x64 tile, 16-deep slices, every output summed by one thread over k ascending.
@@ -168,14 +168,14 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256) gemm_batched_kernel(TO* __restrict__ out, const TA* __restrict__ x, const TW* __restrict__ w,
                                                            const float* __restrict__ bias, const int* __restrict__ tile_batch, int M, int N, int K,
                                                            long long ldx, long long x_batch, long long ldw, long long w_batch, long long ldo,
-                                                           long long out_batch, long long bias_batch, int act) {
+                                                           long long out_batch, long long bias_batch, int act, int tile_rows) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   pdl_begin();
   int b = blockIdx.z;
   if (tile_batch) {
-    b = tile_batch[blockIdx.y];
+    b = tile_batch[blockIdx.y * 64 / tile_rows];  // tile_rows is a multiple of this kernel's 64 rows
     if (b < 0) return;
     w += (size_t)b * w_batch;
     if (bias) bias += (size_t)b * bias_batch;
@@ -235,22 +235,22 @@ __global__ void __launch_bounds__(256) gemm_batched_kernel(TO* __restrict__ out,
 template <typename TA, typename TW, typename TO>
 static int gemm_batched_launch(void* out, const void* x, const void* w, const float* bias, const int* tile_batch, int batches, int M, int N, int K,
                                long long ldx, long long x_batch, long long ldw, long long w_batch, long long ldo, long long out_batch,
-                               long long bias_batch, int act, cudaStream_t stream) {
+                               long long bias_batch, int act, int tile_rows, cudaStream_t stream) {
   dim3 grid((N + 63) / 64, (M + 63) / 64, tile_batch ? 1 : batches);
   launch_dep(gemm_batched_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, (TO*)out, (const TA*)x, (const TW*)w, bias, tile_batch, M, N, K, ldx,
-             x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act);
+             x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act, tile_rows);
   return launch_status();
 }
 
 // dtype flags: 0 = fp32, 1 = bf16.  x and w share a dtype flag pair as in alofa_gemm_generic.
 ALOFA_API int alofa_gemm_batched(void* out, const void* x, const void* w, const float* bias, const int* tile_batch, int batches, int M, int N, int K,
                                  long long ldx, long long x_batch, long long ldw, long long w_batch, long long ldo, long long out_batch,
-                                 long long bias_batch, int act, int x_bf16, int w_bf16, int out_bf16, cudaStream_t stream) {
+                                 long long bias_batch, int act, int tile_rows, int x_bf16, int w_bf16, int out_bf16, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || batches <= 0) return ALOFA_OK;
-  if (K <= 0 || (M + 63) / 64 > 65535 || batches > 65535) return ALOFA_ERR_ARGUMENT;
+  if (K <= 0 || (M + 63) / 64 > 65535 || batches > 65535 || (tile_batch && (tile_rows <= 0 || tile_rows % 64))) return ALOFA_ERR_ARGUMENT;
   const int key = (x_bf16 ? 4 : 0) | (w_bf16 ? 2 : 0) | (out_bf16 ? 1 : 0);
 #define ALOFA_BATCHED(TA, TW, TO) \
-  return gemm_batched_launch<TA, TW, TO>(out, x, w, bias, tile_batch, batches, M, N, K, ldx, x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act, stream)
+  return gemm_batched_launch<TA, TW, TO>(out, x, w, bias, tile_batch, batches, M, N, K, ldx, x_batch, ldw, w_batch, ldo, out_batch, bias_batch, act, tile_rows, stream)
   switch (key) {
     case 0: ALOFA_BATCHED(float, float, float);
     case 1: ALOFA_BATCHED(float, float, bf16);
@@ -593,13 +593,22 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
   extern __shared__ __align__(16) uint8_t router_smem[];
   const int cols = E + (gated ? 1 : 0);
   float* z = reinterpret_cast<float*>(router_smem);      // [TT][cols]
-  T* xs = reinterpret_cast<T*>(z + TT * cols + ((TT * cols) & 1));  // [TT][hidden]
+  T* xs = reinterpret_cast<T*>(z + ((TT * cols + 3) & ~3));  // [TT][hidden], on a 16-byte boundary
   pdl_begin();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TT;
   const int live = min(TT, T_ - t0);
-  for (int r = 0; r < TT; ++r)
-    for (int c = threadIdx.x; c < hidden; c += 256) xs[r * hidden + c] = r < live ? x[(size_t)(t0 + r) * hidden + c] : from_f<T>(0.f);
+  if ((hidden * sizeof(T)) % 16 == 0) {  // rows start on 16-byte boundaries: 16 bytes a thread
+    constexpr int PER = 16 / sizeof(T);
+    const int chunks = hidden / PER;
+    for (int e = threadIdx.x; e < TT * chunks; e += 256) {
+      const int r = e / chunks, c = e - r * chunks;
+      reinterpret_cast<uint4*>(xs)[e] = r < live ? reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * hidden)[c] : make_uint4(0, 0, 0, 0);
+    }
+  } else {
+    for (int r = 0; r < TT; ++r)
+      for (int c = threadIdx.x; c < hidden; c += 256) xs[r * hidden + c] = r < live ? x[(size_t)(t0 + r) * hidden + c] : from_f<T>(0.f);
+  }
   __syncthreads();
   for (int e = warp; e < cols; e += 8) {
     const float* w = wr + (size_t)e * hidden;
@@ -681,7 +690,7 @@ template <typename T, int TT>
 static int moe_router_launch(int* choice, float* weight, float* gate, const void* x, const float* wr, int T_, int E, int top, int hidden, int softmax,
                              int renormalize, cudaStream_t stream) {
   const int cols = E + (gate ? 1 : 0);
-  const size_t smem = ((size_t)TT * cols + 1) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
+  const size_t smem = ((size_t)TT * cols + 4) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
   static size_t set = 0;
   if (smem > set) {
     if (cudaFuncSetAttribute(moe_router_kernel<T, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
@@ -698,7 +707,8 @@ ALOFA_API int alofa_moe_router(int* choice, float* weight, float* gate, const vo
   if (E <= 0 || top <= 0 || top > E || top > 32) return ALOFA_ERR_ARGUMENT;
   const size_t row = (size_t)hidden * (x_bf16 ? 2 : 4) + (size_t)(E + 1) * 4;
   const size_t room = 200 * 1024;
-  if (8 * row <= room)
+  // few tokens: two to a block, so that a decode step's tokens are spread over more than a handful of SMs
+  if (8 * row <= room && T > 512)
     return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream)
                   : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream);
   if (2 * row <= room)

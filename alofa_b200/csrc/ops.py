@@ -72,7 +72,7 @@ def _gemm_tc():
     if lib is None:
         lib = load_library("alofa_gemm_tc", ["kernels/gemm_tc.cu"])
         lib.alofa_gemm_tc.restype = _I
-        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P]
+        lib.alofa_gemm_tc.argtypes = [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _I, _P]
         lib.alofa_splitk_reduce.restype = _I
         lib.alofa_splitk_reduce.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _P]
         lib.alofa_gemm_tc_reduces_in_cluster.restype = _I
@@ -343,7 +343,8 @@ def gemm_tc_splits(k: int, splits: int) -> int:
 B_ROWS, B_MERGED_SPLITS, B_NORMED = 0, 1, 2
 
 
-def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None, acc=None, act: int = 0) -> bool:
+def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, status=None, reduce: bool = True, computed=None, acc=None, act: int = 0,
+            tile_batch=None, batches: int = 1) -> bool:
     """Tensor-core product ``out = x @ w.T`` (bf16 operands, fp32 sums) with
     the epilogue fused.  Returns False, having launched nothing, when the
     kernel does not take these sizes (depth not a multiple of 8, unaligned).
@@ -361,9 +362,13 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     instead of into ``out``; nothing else is written.
 
     ``act`` (EPI_STORE only): a code of ``ACTIVATIONS`` applied to the fp32
-    sums plus bias before they are stored."""
+    sums plus bias before they are stored.
+
+    ``tile_batch`` (int32 on the device; tokens on M, EPI_STORE, no bias):
+    ``w`` is [batches * N, K] and the i-th tile of 128 token rows multiplies
+    by the rows of batch ``tile_batch[i]``; a negative entry skips the tile."""
     n = out.shape[1]
-    rows_w = 2 * n if epi == EPI_GATED else n
+    rows_w = (2 * n if epi == EPI_GATED else n) * (batches if tile_batch is not None else 1)
     k = w.shape[1]
     m = out.shape[0]
     if w.shape[0] != rows_w or (x is not None and tuple(x.shape) != (m, k)) or (bias is not None and bias.shape[0] != rows_w):
@@ -391,7 +396,8 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
         m, n, k, epi | (act << 4), _is_bf16(out, "out"), bn, splits, 1 if reduce else 0,
         _dev(status, "status", torch.int32) if status is not None else None,
         b_kind, b_src, b_ml, b_pos, heads, hd, window, split_keys,
-        _dev(acc, "acc", i64) if acc is not None else None, n_acc, n_gamma, float(n_eps), n_out, n_zero, _stream(),
+        _dev(acc, "acc", i64) if acc is not None else None, n_acc, n_gamma, float(n_eps), n_out, n_zero,
+        _dev(tile_batch, "tile_batch", torch.int32) if tile_batch is not None else None, batches, _stream(),
     )
     if rc == 1:
         return False
@@ -547,8 +553,8 @@ def _latent():
             "alofa_latent_prepare": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
             "alofa_latent_query_turn": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rotary_interleaved": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_gemm_batched": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _P],
-            "alofa_gemm_batched_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _P],
+            "alofa_gemm_batched": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _I, _I, _P],
+            "alofa_gemm_batched_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _L, _L, _L, _I, _I, _I, _P],
             "alofa_activate": [_P, _P, _P, _L, _I, _I, _I, _P],
             "alofa_latent_attention": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
             "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
@@ -616,12 +622,12 @@ def rotary_interleaved(x, freq, positions, heads: int, hd: int, rot_dims: int) -
 
 
 def gemm_batched(out, x, w, batches: int, m: int, n: int, k: int, ldx: int, x_batch: int, ldw: int, w_batch: int, ldo: int, out_batch: int,
-                 bias=None, bias_batch: int = 0, act: str = "none", tile_batch=None) -> None:
+                 bias=None, bias_batch: int = 0, act: str = "none", tile_batch=None, tile_rows: int = 64) -> None:
     """``out_b[m, n] = act(x_b[m, :] . w_b[n, :] + bias_b[n])`` for every batch
     b, operands addressed by row and batch strides (in elements) from the
-    tensors' first elements.  With ``tile_batch`` (int32, one entry per 64-row
-    tile) there is one x and one out and tile i uses the weight of batch
-    ``tile_batch[i]``; negative entries are skipped.  bfloat16 operands whose
+    tensors' first elements.  With ``tile_batch`` (int32, one entry per tile of
+    ``tile_rows`` rows, a multiple of 64) there is one x and one out and tile i
+    uses the weight of batch ``tile_batch[i]``; negative entries are skipped.  bfloat16 operands whose
     depth and strides are multiples of 8 go to the tensor-core kernel, all
     others to the one that takes every size."""
     for t, name in ((out, "out"), (x, "x"), (w, "w")):
@@ -634,7 +640,7 @@ def gemm_batched(out, x, w, batches: int, m: int, n: int, k: int, ldx: int, x_ba
             _latent().alofa_gemm_batched_bf16(
                 out.data_ptr(), x.data_ptr(), w.data_ptr(), _dev(bias, "bias", torch.float32) if bias is not None else None,
                 _dev(tile_batch, "tile_batch", torch.int32) if tile_batch is not None else None, batches, m, n, k, ldx, x_batch, ldw, w_batch, ldo, out_batch,
-                bias_batch, ACTIVATIONS[act], _is_bf16(out, "out"), _stream(),
+                bias_batch, ACTIVATIONS[act], tile_rows, _is_bf16(out, "out"), _stream(),
             ),
             "gemm_batched_bf16", f"batches={batches} M={m} N={n} K={k}",
         )
@@ -643,7 +649,7 @@ def gemm_batched(out, x, w, batches: int, m: int, n: int, k: int, ldx: int, x_ba
         _latent().alofa_gemm_batched(
             out.data_ptr(), x.data_ptr(), w.data_ptr(), _dev(bias, "bias", torch.float32) if bias is not None else None,
             _dev(tile_batch, "tile_batch", torch.int32) if tile_batch is not None else None, batches, m, n, k, ldx, x_batch, ldw, w_batch, ldo, out_batch,
-            bias_batch, ACTIVATIONS[act], _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
+            bias_batch, ACTIVATIONS[act], tile_rows, _is_bf16(x, "x"), _is_bf16(w, "w"), _is_bf16(out, "out"), _stream(),
         ),
         "gemm_batched", f"batches={batches} M={m} N={n} K={k}",
     )
@@ -698,6 +704,23 @@ def concat_rows(out, a, b) -> None:
 
 
 MOE_TILE = 64  # rows per tile of the sorted matrix: every expert's rows are padded to whole tiles
+MOE_TILE_TC = 128  # the same where the tcgen05 product takes the tiles (its token tile)
+
+
+def gemm_by_tile(out, x, w, tile_batch, tile_rows: int, act: str = "none") -> None:
+    """``out[rows of tile i] = act(x[rows of tile i] @ w[tile_batch[i]].T)``: x
+    [rows, K], w [batches, N, K], out [rows, N], tiles of ``tile_rows`` rows.
+    bfloat16 operands in tiles of 128 rows go to the tcgen05 product with the
+    tokens on the M side (the tile's batch is an offset into the stacked
+    weight's rows), all else to :func:`gemm_batched`."""
+    batches, n, k = w.shape
+    rows = x.shape[0]
+    if (tile_rows == MOE_TILE_TC and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and rows % 128 == 0
+            and os.environ.get("ALOFA_BY_TILE_TC", "1") != "0"):
+        wide = -256 if n > 128 else -128
+        if gemm_tc(out, x, w.view(batches * n, k), None, EPI_STORE, wide, act=ACTIVATIONS[act], tile_batch=tile_batch, batches=batches):
+            return
+    gemm_batched(out, x, w, 1, rows, n, k, k, 0, k, n * k, n, 0, act=act, tile_batch=tile_batch, tile_rows=tile_rows)
 
 
 def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = False, renormalize: bool = False) -> None:

@@ -12,8 +12,9 @@ wsg^T)`` when ``shared_gate`` is set.
 Nothing here asks the host: the tokens' choices stay on the device.  The
 (token, choice) pairs are sorted by expert into a matrix in which every expert's
 rows are padded to whole tiles, so one launch per projection multiplies each
-tile by its expert's weights; the outputs are gathered back and added in the
-order of the choices."""
+tile by its expert's weights (in bfloat16 the tcgen05 product with the tokens on
+the M side: a tile's expert is an offset into the stacked weight's rows); the
+outputs are gathered back and added in the order of the choices."""
 from __future__ import annotations
 
 import torch
@@ -76,10 +77,12 @@ class RoutedExperts(Part):
             self.shared.load(state)
 
     def scratch_row_bytes(self) -> int:
-        return self.top * (4 * self.hidden + 4 * self.ff + 4 * self.hidden) + 8 * self.hidden + 4 * self.shared_ff + 4 * (self.experts + 1)
+        return 2 * self.top * (4 * self.hidden + 4 * self.ff + 4 * self.hidden) + 8 * self.hidden + 4 * self.shared_ff + 4 * (self.experts + 1)
 
     def forward(self, ctx, x, h, store=False):
-        n, dt, top, tile = x.shape[0], self.rt.dtype, self.top, ops.MOE_TILE
+        n, dt, top = x.shape[0], self.rt.dtype, self.top
+        # tiles of 128 rows where the tcgen05 product takes them (bfloat16, depths that are multiples of 8), else of 64
+        tile = ops.MOE_TILE_TC if dt == torch.bfloat16 and self.hidden % 8 == 0 and self.ff % 8 == 0 else ops.MOE_TILE
         i32, f32 = torch.int32, torch.float32
         choice, weight = ctx.buf((n, top), i32), ctx.buf((n, top), f32)
         gate = ctx.buf((n,), f32) if self.shared_gate else None
@@ -92,10 +95,9 @@ class RoutedExperts(Part):
         xs = ctx.buf((rows, self.hidden), dt)
         ops.moe_scatter(xs, x, weight if self.weight_on_input else None, dest, top)
         mid = ctx.buf((rows, self.ff), dt)
-        ops.gemm_batched(mid, xs, self.up, 1, rows, self.ff, self.hidden, self.hidden, 0, self.hidden, self.ff * self.hidden, self.ff, 0,
-                         act=self.act, tile_batch=tile_expert)
+        ops.gemm_by_tile(mid, xs, self.up, tile_expert, tile, act=self.act)
         ys = ctx.buf((rows, self.hidden), f32)
-        ops.gemm_batched(ys, mid, self.down, 1, rows, self.hidden, self.ff, self.ff, 0, self.ff, self.hidden * self.ff, self.hidden, 0, tile_batch=tile_expert)
+        ops.gemm_by_tile(ys, mid, self.down, tile_expert, tile)
         shared = None
         if self.shared is not None:
             shared = ctx.buf((n, self.hidden), f32)

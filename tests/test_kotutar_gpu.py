@@ -353,6 +353,29 @@ def test_batched_products_with_strides_and_by_tile(dtype):
             assert_close(got[rows], plain.gelu_erf(x[rows] @ w[e].T), 1e-5 if dtype == F32 else 2e-3, f"tile {i} (expert {e})")
 
 
+@pytest.mark.parametrize("hidden,ff", [(64, 72), (128, 320), (256, 100)])
+def test_products_by_tile_on_the_tcgen05_kernel(hidden, ff):
+    """bfloat16 tiles of 128 rows, each with the weight its tile names (one named twice, one never, two
+    tiles empty), with and without an activation, stored as bfloat16 and as fp32."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(11)
+    experts = 5
+    tile_expert = np.array([3, 3, 0, -1, 4, 1, -1], dtype=np.int32)
+    x = rounded(rng.standard_normal((len(tile_expert) * 128, hidden)), BF16)
+    w = rounded(rng.standard_normal((experts, ff, hidden)) / np.sqrt(hidden), BF16)
+    for act, fn, out_dtype in (("gelu_erf", plain.gelu_erf, BF16), ("none", lambda z: z, F32)):
+        out = torch.full((len(x), ff), 5.0, dtype=out_dtype, device="cuda")
+        ops.gemm_by_tile(out, dev(x, BF16), dev(w, BF16), dev(tile_expert), 128, act=act)
+        got = out.float().cpu().numpy()
+        for i, e in enumerate(tile_expert):
+            rows = slice(128 * i, 128 * i + 128)
+            if e < 0:
+                assert (got[rows] == 5.0).all(), "a tile that names no expert was written"
+            else:
+                assert_close(got[rows], fn(x[rows] @ w[e].T), KERNEL_TOL[BF16] if out_dtype == BF16 else 2e-3, f"tile {i} (expert {e}) act={act}")
+
+
 # ---------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------
