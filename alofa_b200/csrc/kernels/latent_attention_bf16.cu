@@ -9,12 +9,14 @@
 // in blocks of 32 rows of the paged cache (cp.async, a ring of blocks); the same
 // block in shared memory is the key operand (all D columns) and the value
 // operand (its first KV_RANK columns).  Eight warps: warp = (row group of 16
-// rows, half of the value columns).  Both halves of a row group compute the
-// group's scores S = Q K^T (mma.sync m16n8k16, fp32 sums over D), take the
-// streaming softmax in fp32 in registers (maximum, sum, exp2 of scores scaled by
-// scale * log2 e), round the weights to bfloat16 in the A-fragment layout, and
-// each adds P V for its half of the columns into fp32 accumulators in registers
-// (KV_RANK / 4 per thread).  The sink enters as the initial state of a row:
+// rows, half of the value columns).  The two warps of a row group share the
+// group's scores S = Q K^T (mma.sync m16n8k16, fp32 sums over D): each takes 16
+// of the block's 32 keys, they exchange the rows' maxima through shared memory
+// behind a two-warp barrier, take the streaming softmax in fp32 in registers
+// (exp2 of scores scaled by scale * log2 e), round the weights to bfloat16 -
+// one warp's 16 keys are exactly one A fragment of the second product -,
+// exchange fragments and sums, and each adds P V for its half of the columns
+// into fp32 accumulators in registers (KV_RANK / 4 per thread).  The sink enters as the initial state of a row:
 // maximum = sink, sum = 1, nothing added to the output.
 //
 // Causal bound and window go by the row's own position; keys past the request's
@@ -62,6 +64,9 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ void cp16(uint32_t dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src)); }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+constexpr int XCHG_BYTES = 2 * 16 * 4 + 2 * 16 * 4 + 2 * 32 * 16;  // per row group
+// the two warps of row group `rg` meet (named barriers 1..4; barrier 0 is the block's)
+__device__ __forceinline__ void pair_sync(int rg) { asm volatile("bar.sync %0, 64;" ::"r"(rg + 1) : "memory"); }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -77,6 +82,11 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [BM][PITCH]
   bf16* Ks = Qs + BM * PITCH;                        // [STAGES][BN][PITCH]
+  // what the two warps of a row group hand one another per key block: maxima and sums of their 16 keys per row, their weight fragments
+  uint8_t* xchg = reinterpret_cast<uint8_t*>(Ks + (size_t)STAGES * BN * PITCH) + (size_t)((threadIdx.x >> 5) % GROUPS) * XCHG_BYTES;
+  float* x_max = reinterpret_cast<float*>(xchg);           // [2][16]
+  float* x_sum = x_max + 32;                                // [2][16]
+  uint4* x_frag = reinterpret_cast<uint4*>(x_sum + 32);     // [2][32]
   pdl_begin();
   const int seq = blockIdx.y, tile = blockIdx.x;
   const int t0 = q_start[seq], q_len = q_start[seq + 1] - t0;
@@ -164,56 +174,69 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
       __syncthreads();
       continue;
     }
-    // S = Q K^T for 16 rows x 32 keys
-    float s[4][4];
+    // S = Q K^T for 16 rows x this warp's 16 keys of the block (the group's other warp takes the other 16)
+    float s[2][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) s[j][k] = 0.f;
-    const uint32_t k_base = smem_addr(Kb + ((lane & 7) + (lane >> 4) * 8) * PITCH + ((lane >> 3) & 1) * 8);
+    const uint32_t k_base = smem_addr(Kb + (ch * 16 + (lane & 7) + (lane >> 4) * 8) * PITCH + ((lane >> 3) & 1) * 8);
 #pragma unroll 4
     for (int k0 = 0; k0 < D; k0 += 16) {
-      uint32_t a[4], b01[4], b23[4];
+      uint32_t a[4], kb[4];
       ldsm4(a, q_base + k0 * 2);
-      ldsm4(b01, k_base + k0 * 2);
-      ldsm4(b23, k_base + (16 * PITCH + k0) * 2);
-      mma16816(s[0], a, b01[0], b01[1]);
-      mma16816(s[1], a, b01[2], b01[3]);
-      mma16816(s[2], a, b23[0], b23[1]);
-      mma16816(s[3], a, b23[2], b23[3]);
+      ldsm4(kb, k_base + k0 * 2);
+      mma16816(s[0], a, kb[0], kb[1]);
+      mma16816(s[1], a, kb[2], kb[3]);
     }
-    // mask, streaming softmax (in units of log2)
+    // mask; the rows' maxima over the warp's keys, then over the group's (in units of log2)
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int i = k >> 1;
-        const int key = b * BN + j * 8 + 2 * t + (k & 1);
+        const int key = b * BN + ch * 16 + j * 8 + 2 * t + (k & 1);
         const float v = (key <= pos[i] && key >= first[i]) ? s[j][k] * scale_log2 : -INFINITY;
         s[j][k] = v;
         mx[i] = fmaxf(mx[i], v);
       }
-    float corr[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      const float m_new = fmaxf(m[i], mx[i]);
+      if (t == 0) x_max[ch * 16 + g + 8 * i] = mx[i];
+    }
+    pair_sync(rg);
+    float corr[2], sum[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float m_new = fmaxf(m[i], fmaxf(mx[i], x_max[(ch ^ 1) * 16 + g + 8 * i]));
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       corr[i] = exp2f(m[i] - m_use);  // m = -inf: 0
       m[i] = m_new;
-      float sum = 0.f;
+      sum[i] = 0.f;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 2; ++j) {
         s[j][2 * i] = exp2f(s[j][2 * i] - m_use);
         s[j][2 * i + 1] = exp2f(s[j][2 * i + 1] - m_use);
-        sum += s[j][2 * i] + s[j][2 * i + 1];
+        sum[i] += s[j][2 * i] + s[j][2 * i + 1];
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l[i] = l[i] * corr[i] + sum;
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      if (t == 0) x_sum[ch * 16 + g + 8 * i] = sum[i];
     }
+    // the weights of the warp's 16 keys, rounded, are one A fragment of the second product: both warps need both
+    uint4 mine;
+    mine.x = pack2(s[0][0], s[0][1]);
+    mine.y = pack2(s[0][2], s[0][3]);
+    mine.z = pack2(s[1][0], s[1][1]);
+    mine.w = pack2(s[1][2], s[1][3]);
+    x_frag[ch * 32 + lane] = mine;
+    pair_sync(rg);
+    const uint4 other = x_frag[(ch ^ 1) * 32 + lane];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) l[i] = l[i] * corr[i] + (x_sum[g + 8 * i] + x_sum[16 + g + 8 * i]);  // keys 0-15 first, in both warps
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       o[j][0] *= corr[0];
@@ -221,15 +244,12 @@ latent_attention_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ qa
       o[j][2] *= corr[1];
       o[j][3] *= corr[1];
     }
-    // O += P V over this warp's half of the value columns
+    // O += P V over this warp's half of the value columns, all 32 keys
     const uint32_t v_base = smem_addr(Kb + ((lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + ch * HALF + (lane >> 4) * 8);
 #pragma unroll
     for (int kk = 0; kk < 2; ++kk) {
-      uint32_t p[4];
-      p[0] = pack2(s[2 * kk][0], s[2 * kk][1]);
-      p[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
-      p[2] = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-      p[3] = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      const uint4 f = kk == ch ? mine : other;
+      const uint32_t p[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
       for (int j = 0; j < NT; j += 2) {
         uint32_t v[4];
@@ -294,11 +314,11 @@ ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void*
   if (splits > 1 && (!part_o || !part_ml || blocks_per_split <= 0 || total_rows <= 0 || splits > 65535)) return ALOFA_ERR_ARGUMENT;
   const bool narrow = (long long)max_q_len * heads <= 16;
   const int bm = narrow ? 16 : 64, stages = narrow ? 2 : 3;
-  const size_t smem = (size_t)(bm + stages * BN) * PITCH * sizeof(bf16);
+  const size_t smem = (size_t)(bm + stages * BN) * PITCH * sizeof(bf16) + (size_t)(narrow ? 1 : 4) * XCHG_BYTES;
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(latent_attention_bf16_kernel<4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((64 + 3 * BN) * PITCH * sizeof(bf16))) != cudaSuccess ||
-        cudaFuncSetAttribute(latent_attention_bf16_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((16 + 2 * BN) * PITCH * sizeof(bf16))) != cudaSuccess)
+    if (cudaFuncSetAttribute(latent_attention_bf16_kernel<4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((64 + 3 * BN) * PITCH * sizeof(bf16) + 4 * XCHG_BYTES)) != cudaSuccess ||
+        cudaFuncSetAttribute(latent_attention_bf16_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((16 + 2 * BN) * PITCH * sizeof(bf16) + XCHG_BYTES)) != cudaSuccess)
       return ALOFA_ERR_LAUNCH;
     set = true;
   }
@@ -319,5 +339,5 @@ ALOFA_API int alofa_latent_attention_bf16(void* out, const void* qa, const void*
 ALOFA_API int alofa_latent_attention_bf16_sizes(int* kv_rank, int* rot) {
   *kv_rank = KV_RANK;
   *rot = ROT;
-  return (int)((64 + 3 * BN) * PITCH * sizeof(bf16));
+  return (int)((64 + 3 * BN) * PITCH * sizeof(bf16) + 4 * XCHG_BYTES);
 }

@@ -780,7 +780,7 @@ def latent_attention_bf16_supported(kv_rank: int, rot: int) -> bool:
     value columns and for the row width, accumulators that fit the registers,
     tiles that fit shared memory."""
     width = kv_rank + rot
-    return kv_rank % 32 == 0 and width % 16 == 0 and 32 <= kv_rank <= 512 and (64 + 3 * 32) * (width + 8) * 2 <= 220 * 1024
+    return kv_rank % 32 == 0 and width % 16 == 0 and 32 <= kv_rank <= 512 and (64 + 3 * 32) * (width + 8) * 2 + 4 * 1280 <= 220 * 1024
 
 
 def _latent_attention_lib(kv_rank: int, rot: int):
