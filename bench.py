@@ -27,7 +27,7 @@ JSON line is printed:
 
 Method, after the reference's own benchmark (src/alofa/cli.mojo:62-82,
 819-850): warm-up first, then every repetition timed on its own and the median
-reported with the span; ``value`` itself is the contract's figure, K steps
+reported with the span; ``value`` itself is the time of K steps
 between one pair of events.
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from

@@ -155,7 +155,7 @@ def run_latent_attention_tc(qa, cache, table, sink, lengths, portions, heads, kv
     return out.float().cpu().numpy().reshape(-1, heads, kv_rank), q_start
 
 
-@pytest.mark.parametrize("heads,kv_rank,rot,window,sunk", [(3, 64, 16, None, True), (10, 32, 16, 37, True), (16, 128, 32, None, False), (5, 96, 0, 16, True), (70, 32, 0, None, True)])
+@pytest.mark.parametrize("heads,kv_rank,rot,window,sunk", [(3, 64, 48, None, True), (10, 32, 16, 37, True), (16, 128, 32, None, False), (5, 96, 0, 16, True), (70, 32, 0, None, True)])
 def test_latent_attention_on_tensor_cores(heads, kv_rank, rot, window, sunk):
     """Whole prompts, portions that end a longer history (2 tokens, a page and a bit), and single decode
     tokens, at lengths around the borders of pages (16), key blocks (32) and row tiles (64 rows of
