@@ -39,11 +39,20 @@ class StateCache:
     state: torch.Tensor
 
 
+def flat_specs(plan: dict) -> list:
+    """Every cache spec of a plan, the members of tuples (mixers made of
+    several side by side) taken one by one."""
+    out = []
+    for spec in plan.values():
+        out.extend(spec if isinstance(spec, (tuple, list)) else [spec])
+    return out
+
+
 def group_windows(plan: dict) -> list:
     """The distinct windows of a cache plan, all-keys (None) first; empty when
     no layer wants pages (the model then has state slots only, and neither the
     cache manager nor the scheduler books a page for it)."""
-    windows = {spec.window for spec in plan.values() if isinstance(spec, (PagedKV, PagedRows))}
+    windows = {spec.window for spec in flat_specs(plan) if isinstance(spec, (PagedKV, PagedRows))}
     return ([None] if None in windows else []) + sorted(w for w in windows if w is not None)
 
 
@@ -55,46 +64,53 @@ class CacheStorage:
         self.groups = groups
         self.caches = {}
         self.bytes = 0
+        self.device, self.dtype, self.max_requests = device, dtype, max_requests
+        self._windows = windows
+        self._states = []
         for idx, spec in plan.items():
-            if isinstance(spec, PagedKV):
-                if spec.window not in windows:
-                    raise AlofaError("invalid_argument", "no cache group for this window", f"window={spec.window} groups={windows}")
-                gi = windows.index(spec.window)
-                g = groups[gi]
-                shape = (g.num_pages * g.block_size, spec.num_kv_heads, spec.head_dim)
-                k = torch.zeros(shape, dtype=dtype, device=device)
-                v = torch.zeros(shape, dtype=dtype, device=device)
-                self.caches[idx] = LayerCache(gi, k, v)
-                self.bytes += 2 * k.numel() * k.element_size()
-            elif isinstance(spec, PagedRows):
-                if spec.window not in windows:
-                    raise AlofaError("invalid_argument", "no cache group for this window", f"window={spec.window} groups={windows}")
-                gi = windows.index(spec.window)
-                g = groups[gi]
-                rows = torch.zeros((g.num_pages * g.block_size, spec.width), dtype=dtype, device=device)
-                self.caches[idx] = LayerCache(gi, rows, None)
-                self.bytes += rows.numel() * rows.element_size()
-            elif isinstance(spec, SlotState):
-                st = torch.zeros((max_requests,) + tuple(spec.shape), dtype=spec.dtype, device=device)
-                self.caches[idx] = StateCache(st)
-                self.bytes += st.numel() * st.element_size()
+            if isinstance(spec, (tuple, list)):  # a mixer made of several: the tuple of their caches
+                self.caches[idx] = tuple(self._make(idx, one) for one in spec)
             elif spec is not None:
-                raise AlofaError("unsupported", "unknown cache spec", f"entry={idx} spec={spec!r}")
+                self.caches[idx] = self._make(idx, spec)
+
+    def _make(self, idx, spec):
+        windows, groups, dtype, device = self._windows, self.groups, self.dtype, self.device
+        if isinstance(spec, (PagedKV, PagedRows)):
+            if spec.window not in windows:
+                raise AlofaError("invalid_argument", "no cache group for this window", f"window={spec.window} groups={windows}")
+            gi = windows.index(spec.window)
+            g = groups[gi]
+            if isinstance(spec, PagedKV):
+                slots = g.num_pages * g.block_size
+                k = torch.zeros((slots, spec.num_kv_heads, spec.head_dim), dtype=dtype, device=device)
+                v = torch.zeros((slots, spec.num_kv_heads, spec.v_head_dim or spec.head_dim), dtype=dtype, device=device)
+                self.bytes += (k.numel() + v.numel()) * k.element_size()
+                return LayerCache(gi, k, v)
+            rows = torch.zeros((g.num_pages * g.block_size, spec.width), dtype=dtype, device=device)
+            self.bytes += rows.numel() * rows.element_size()
+            return LayerCache(gi, rows, None)
+        if isinstance(spec, SlotState):
+            st = torch.zeros((self.max_requests,) + tuple(spec.shape), dtype=spec.dtype, device=device)
+            self.bytes += st.numel() * st.element_size()
+            self._states.append(st)
+            return StateCache(st)
+        if spec is None:
+            return None
+        raise AlofaError("unsupported", "unknown cache spec", f"entry={idx} spec={spec!r}")
 
     def reset_slot(self, slot: int) -> None:
         """Zero the fixed-size state of a slot when a request starts in it."""
-        for cache in self.caches.values():
-            if isinstance(cache, StateCache):
-                cache.state[slot].zero_()
+        for state in self._states:
+            state[slot].zero_()
 
     @staticmethod
     def bytes_per_token(plan: dict, dtype: torch.dtype) -> dict:
         """window -> bytes of paged cache one token takes in that group."""
         width = torch.empty((), dtype=dtype).element_size()
         out = {}
-        for spec in plan.values():
+        for spec in flat_specs(plan):
             if isinstance(spec, PagedKV):
-                out[spec.window] = out.get(spec.window, 0) + 2 * spec.num_kv_heads * spec.head_dim * width
+                out[spec.window] = out.get(spec.window, 0) + spec.num_kv_heads * (spec.head_dim + (spec.v_head_dim or spec.head_dim)) * width
             elif isinstance(spec, PagedRows):
                 out[spec.window] = out.get(spec.window, 0) + spec.width * width
         return out

@@ -276,13 +276,15 @@ ALOFA_API int alofa_rope_store(void* q_out, void* k_cache, void* v_cache, const 
 // block_table[r][j / page_size].  Keys are taken in chunks of 128 whose
 // boundaries depend on the key index only; within a chunk each thread scores
 // one key, the block takes max and sum in a fixed order, and the value sum is
-// rescaled as in streaming softmax.  score = dot * scale, all in fp32.
+// rescaled as in streaming softmax.  score = dot * scale, then (softcap > 0)
+// softcap * tanh(score / softcap), all in fp32.  Keys have hd numbers per head,
+// values vd (the two caches have their own row widths).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
-    int max_blocks, int page_size, int nh, int nkv, int hd, int window, float scale) {
+    int max_blocks, int page_size, int nh, int nkv, int hd, int vd, int window, float scale, float softcap) {
   extern __shared__ float smem[];
   float* qs = smem;          // hd
   float* ps = smem + hd;     // 128
@@ -310,6 +312,7 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_f(kr[d]), dot);
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     pages[tid] = slot;
     const float cmax = block_max(s, scratch);
@@ -325,34 +328,34 @@ __global__ void __launch_bounds__(128) paged_attention_generic_kernel(
     for (int i = 0; i < n_in; ++i) {
       const int sl = pages[i];
       if (sl < 0) continue;
-      const T* vr = v_cache + ((size_t)sl * nkv + kvh) * hd;
+      const T* vr = v_cache + ((size_t)sl * nkv + kvh) * vd;
       const float pi = ps[i];
-      if (tid < hd) acc0 = fmaf(pi, to_f(vr[tid]), acc0);
-      if (tid + 128 < hd) acc1 = fmaf(pi, to_f(vr[tid + 128]), acc1);
+      if (tid < vd) acc0 = fmaf(pi, to_f(vr[tid]), acc0);
+      if (tid + 128 < vd) acc1 = fmaf(pi, to_f(vr[tid + 128]), acc1);
     }
     m = m_new;
     __syncthreads();
   }
-  T* o = out + ((size_t)t * nh + h) * hd;
-  if (tid < hd) o[tid] = from_f<T>(acc0 / l);
-  if (tid + 128 < hd) o[tid + 128] = from_f<T>(acc1 / l);
+  T* o = out + ((size_t)t * nh + h) * vd;
+  if (tid < vd) o[tid] = from_f<T>(acc0 / l);
+  if (tid + 128 < vd) o[tid + 128] = from_f<T>(acc1 / l);
 }
 
 ALOFA_API int alofa_paged_attention_generic(void* out, const void* q, const void* k_cache, const void* v_cache,
                                             const int* positions, const int* seq_of_token, const int* block_table,
                                             int max_blocks, int page_size, int n_tokens, int nh, int nkv, int hd,
-                                            int window, float scale, int is_bf16, cudaStream_t stream) {
+                                            int vd, int window, float scale, float softcap, int is_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (hd <= 0 || hd > 256 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
+  if (hd <= 0 || vd <= 0 || vd > 256 || nkv <= 0 || nh % nkv != 0 || page_size <= 0) return ALOFA_ERR_ARGUMENT;
   dim3 grid(n_tokens, nh);
   const size_t smem = (size_t)(hd + 128) * sizeof(float);
   if (is_bf16)
     paged_attention_generic_kernel<bf16><<<grid, 128, smem, stream>>>(
         (bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, window, scale);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap);
   else
     paged_attention_generic_kernel<float><<<grid, 128, smem, stream>>>(
         (float*)out, (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, seq_of_token, block_table,
-        max_blocks, page_size, nh, nkv, hd, window, scale);
+        max_blocks, page_size, nh, nkv, hd, vd, window, scale, softcap);
   return launch_status();
 }

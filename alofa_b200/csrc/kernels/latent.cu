@@ -589,7 +589,8 @@ __global__ void moe_route_kernel(int* __restrict__ choice, float* __restrict__ w
 template <typename T, int TT>
 __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate,
                                                          const T* __restrict__ x, const float* __restrict__ wr, int T_, int E, int top, int hidden,
-                                                         int gated, int softmax, int renormalize) {
+                                                         int gated, int softmax, int renormalize, const float* __restrict__ correction,
+                                                         float renorm_eps) {
   extern __shared__ __align__(16) uint8_t router_smem[];
   const int cols = E + (gated ? 1 : 0);
   float* z = reinterpret_cast<float*>(router_smem);      // [TT][cols]
@@ -662,10 +663,13 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
     __syncwarp();
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
+      // the choice goes by score + correction (when given), the weight is the score itself
       float best = -INFINITY;
       int arg = 0x7fffffff;
-      for (int e = lane; e < E; e += 32)
-        if (s[e] > best) best = s[e], arg = e;
+      for (int e = lane; e < E; e += 32) {
+        const float v = correction ? s[e] + correction[e] : s[e];
+        if (v > best) best = v, arg = e;
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
@@ -673,6 +677,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
         if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
       }
       if (arg >= E) arg = k, best = 0.f;
+      else if (correction) best = s[arg];
+      __syncwarp();
       if (lane == 0) {
         choice[(size_t)t * top + k] = arg;
         weight[(size_t)t * top + k] = best;
@@ -681,14 +687,14 @@ __global__ void __launch_bounds__(256) moe_router_kernel(int* __restrict__ choic
       total += best;
       __syncwarp();
     }
-    if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total;
+    if (renormalize && lane < top) weight[(size_t)t * top + lane] /= total + renorm_eps;
     if (gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zg));
   }
 }
 
 template <typename T, int TT>
 static int moe_router_launch(int* choice, float* weight, float* gate, const void* x, const float* wr, int T_, int E, int top, int hidden, int softmax,
-                             int renormalize, cudaStream_t stream) {
+                             int renormalize, const float* correction, float renorm_eps, cudaStream_t stream) {
   const int cols = E + (gate ? 1 : 0);
   const size_t smem = ((size_t)TT * cols + 4) * sizeof(float) + (size_t)TT * hidden * sizeof(T);
   static size_t set = 0;
@@ -697,23 +703,24 @@ static int moe_router_launch(int* choice, float* weight, float* gate, const void
     set = smem;
   }
   launch_dep(moe_router_kernel<T, TT>, (T_ + TT - 1) / TT, 256, smem, stream, choice, weight, gate, (const T*)x, wr, T_, E, top, hidden, gate ? 1 : 0, softmax,
-             renormalize);
+             renormalize, correction, renorm_eps);
   return launch_status();
 }
 
+// correction (optional, fp32 [E]): added to the scores for the choice only.  renorm_eps: added to the sum the weights are divided by.
 ALOFA_API int alofa_moe_router(int* choice, float* weight, float* gate, const void* x, const float* wr, int T, int E, int top, int hidden, int softmax,
-                               int renormalize, int x_bf16, cudaStream_t stream) {
+                               int renormalize, int x_bf16, const float* correction, float renorm_eps, cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
   if (E <= 0 || top <= 0 || top > E || top > 32) return ALOFA_ERR_ARGUMENT;
   const size_t row = (size_t)hidden * (x_bf16 ? 2 : 4) + (size_t)(E + 1) * 4;
   const size_t room = 200 * 1024;
   // few tokens: two to a block, so that a decode step's tokens are spread over more than a handful of SMs
   if (8 * row <= room && T > 512)
-    return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream)
-                  : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream);
+    return x_bf16 ? moe_router_launch<bf16, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream)
+                  : moe_router_launch<float, 8>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream);
   if (2 * row <= room)
-    return x_bf16 ? moe_router_launch<bf16, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream)
-                  : moe_router_launch<float, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, stream);
+    return x_bf16 ? moe_router_launch<bf16, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream)
+                  : moe_router_launch<float, 2>(choice, weight, gate, x, wr, T, E, top, hidden, softmax, renormalize, correction, renorm_eps, stream);
   return ALOFA_ERR_ARGUMENT;
 }
 
@@ -757,6 +764,8 @@ __global__ void moe_sort_kernel(int* __restrict__ dest, int* __restrict__ tile_e
     for (int i = 0; i < pairs; ++i)
       if (choice[i] == e) dest[i] = at++;
   }
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+    if (choice[i] >= E) dest[i] = -1;  // a choice that is no expert with weights (an identity expert): no row
 }
 
 // The same result faster, for as many experts as shared memory holds a count per thread for: thread i
@@ -773,7 +782,8 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_counted_kernel(int* __r
   const int share = (pairs + SORT_THREADS - 1) / SORT_THREADS;
   const int lo = min(pairs, tid * share), hi = min(pairs, lo + share);
   for (int e = 0; e < E; ++e) counted[e * SORT_THREADS + tid] = 0;
-  for (int i = lo; i < hi; ++i) counted[choice[i] * SORT_THREADS + tid] += 1;
+  for (int i = lo; i < hi; ++i)
+    if (choice[i] < E) counted[choice[i] * SORT_THREADS + tid] += 1;
   __syncthreads();
   // an exclusive sum over the threads, per expert: a warp takes experts in turn, a lane eight threads' counts
   const int warp = tid >> 5, lane = tid & 31;
@@ -813,7 +823,7 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_counted_kernel(int* __r
   __syncthreads();
   for (int i = lo; i < hi; ++i) {
     const int e = choice[i];
-    dest[i] = first[e] + counted[e * SORT_THREADS + tid]++;
+    dest[i] = e < E ? first[e] + counted[e * SORT_THREADS + tid]++ : -1;  // no row for a choice that is no expert with weights
   }
 }
 
@@ -841,6 +851,7 @@ __global__ void moe_scatter_kernel(T* __restrict__ xs, const T* __restrict__ x, 
   pdl_begin();
   const int pair = blockIdx.x, t = pair / top;
   const float w = weight ? weight[pair] : 1.0f;
+  if (dest[pair] < 0) return;
   const size_t to = (size_t)dest[pair] * hidden, from = (size_t)t * hidden;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) xs[to + c] = weight ? from_f<T>(to_f(x[from + c]) * w) : x[from + c];
 }
@@ -854,24 +865,49 @@ ALOFA_API int alofa_moe_scatter(void* xs, const void* x, const float* weight, co
 }
 
 // combine: y[t] = sum_k (weight[t, k] if the weight multiplies the output) * ys[dest[t, k]] + gate[t] * shared[t]  (fp32; k ascending).
+// A pair without a row (dest < 0: an identity expert) contributes the token's own input x[t]; with `add` the sum is added to y.
+template <typename T>
 __global__ void moe_combine_kernel(float* __restrict__ y, const float* __restrict__ ys, const int* __restrict__ dest, const float* __restrict__ weight,
-                                   const float* __restrict__ shared, const float* __restrict__ gate, int top, int hidden) {
+                                   const float* __restrict__ shared, const float* __restrict__ gate, int top, int hidden, const T* __restrict__ x, int add) {
   pdl_begin();
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
-      const float e = ys[(size_t)dest[(size_t)t * top + k] * hidden + c];
+      const int row = dest[(size_t)t * top + k];
+      const float e = row >= 0 ? ys[(size_t)row * hidden + c] : (x ? to_f(x[(size_t)t * hidden + c]) : 0.f);
       v += weight ? weight[(size_t)t * top + k] * e : e;
     }
     if (shared) v += (gate ? gate[t] : 1.0f) * shared[(size_t)t * hidden + c];
-    y[(size_t)t * hidden + c] = v;
+    if (add) y[(size_t)t * hidden + c] += v;
+    else y[(size_t)t * hidden + c] = v;
   }
 }
 
 ALOFA_API int alofa_moe_combine(float* y, const float* ys, const int* dest, const float* weight, const float* shared, const float* gate, int T, int top,
-                                int hidden, cudaStream_t stream) {
+                                int hidden, const void* x, int x_bf16, int add, cudaStream_t stream) {
   if (T <= 0) return ALOFA_OK;
-  launch_dep(moe_combine_kernel, T, 256, 0, stream, y, ys, dest, weight, shared, gate, top, hidden);
+  if (x_bf16) launch_dep(moe_combine_kernel<bf16>, T, 256, 0, stream, y, ys, dest, weight, shared, gate, top, hidden, (const bf16*)x, add);
+  else launch_dep(moe_combine_kernel<float>, T, 256, 0, stream, y, ys, dest, weight, shared, gate, top, hidden, (const float*)x, add);
+  return launch_status();
+}
+
+// mid[r, c] = silu(gu[r, c]) * gu[r, ff + c]: the gated activation of rows that hold [gate | up] side by side (fp32 sums in, compute dtype out).
+template <typename T>
+__global__ void gate_up_kernel(T* __restrict__ mid, const float* __restrict__ gu, long long count, int ff) {
+  pdl_begin();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const long long r = i / ff;
+  const int c = (int)(i - r * ff);
+  const float g = gu[r * 2 * ff + c], u = gu[r * 2 * ff + ff + c];
+  mid[i] = from_f<T>(g / (1.0f + expf(-g)) * u);
+}
+
+ALOFA_API int alofa_gate_up(void* mid, const float* gu, long long rows, int ff, int out_bf16, cudaStream_t stream) {
+  const long long count = rows * ff;
+  if (count <= 0) return ALOFA_OK;
+  if (out_bf16) launch_dep(gate_up_kernel<bf16>, (unsigned)((count + 255) / 256), 256, 0, stream, (bf16*)mid, gu, count, ff);
+  else launch_dep(gate_up_kernel<float>, (unsigned)((count + 255) / 256), 256, 0, stream, (float*)mid, gu, count, ff);
   return launch_status();
 }

@@ -1,0 +1,420 @@
+// Kernels of mixers that carry a state of fixed size from token to token: a short causal
+// convolution per channel, and a linear recurrence over a matrix state per head,
+//
+//   S_t = diag(a_t) S_(t-1) + k_t v_t^T        (S is N x P: N key channels, P value channels)
+//   y_t = S_t^T q_t (+ D v_t)
+//
+// which covers both a state-space layer with one scalar decay per head and token
+// (a_t = exp(-exp(A_log) dt_t) on every row, k_t = dt_t B_t, q_t = C_t) and gated linear attention with
+// one decay per key channel (a_t = sigmoid(z_t)^(1/tau)).  Beside them the norms such mixers end
+// with, an embedding with a scale and a sinusoidal position vector, and the sum of several
+// branches' normed outputs into the residual stream.
+//
+// Everything here is fp32: decays and their logarithms, softplus and exponentials, step sizes, the
+// state, the sums; inputs are the fp32 sums of the projections.  A sequence's tokens are taken one
+// after the other in both prompts and decoding, so a position's result does not depend on how the
+// prompt was cut into steps or on what else is in the batch: for every output element the order of
+// additions is fixed by the sizes alone.
+#include "common.cuh"
+
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, c] = table[id_t, c] * scale + pos(p_t, c), where (freq given) entry 2i of the
+// position vector is sin(p f_i) and entry 2i + 1 is cos(p f_i); the angle is an fp32 product.
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_scaled_kernel(float* __restrict__ out, const TW* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ src,
+                                    const int* __restrict__ fed, const int* __restrict__ positions, const float* __restrict__ freq, int hidden, int vocab,
+                                    float scale, int* status) {
+  pdl_begin();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (src && src[t] >= 0) id = fed[src[t]];
+  const bool ok = id >= 0 && id < vocab;
+  if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+  const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+  const float p = (float)positions[t];
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = ok ? to_f(row[c]) * scale : 0.f;
+    if (freq && ok) {
+      const float ang = p * freq[c >> 1];
+      v += (c & 1) ? cosf(ang) : sinf(ang);
+    }
+    out[(size_t)t * hidden + c] = v;
+  }
+}
+
+ALOFA_API int alofa_embed_scaled(float* out, const void* table, const int* ids, const int* src, const int* fed, const int* positions, const float* freq,
+                                 int n_tokens, int hidden, int vocab, float scale, int table_bf16, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (table_bf16) launch_dep(embed_scaled_kernel<bf16>, n_tokens, 256, 0, stream, out, (const bf16*)table, ids, src, fed, positions, freq, hidden, vocab, scale, status);
+  else launch_dep(embed_scaled_kernel<float>, n_tokens, 256, 0, stream, out, (const float*)table, ids, src, fed, positions, freq, hidden, vocab, scale, status);
+  return launch_status();
+}
+
+// out += x, elementwise (fp32).
+__global__ void add_rows_kernel(float* __restrict__ out, const float* __restrict__ x, long long count) {
+  pdl_begin();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] += x[i];
+}
+
+ALOFA_API int alofa_add_rows(float* out, const float* x, long long count, cudaStream_t stream) {
+  if (count <= 0) return ALOFA_OK;
+  launch_dep(add_rows_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, out, x, count);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Causal convolution per channel with an activation: for channel c of the token at place j of its
+// request, out = silu(bias[c] + sum_l w[c, taps - 1 - l] * in(j - l)), l = 0 .. taps - 1 (the last
+// column of w belongs to the token itself).  Inputs before the step's first token come from the
+// request's state, which holds its last taps - 1 inputs (the newest last; zeros before a request's
+// start).  u [T, ld] fp32, the channels at columns offset ..; out [T, channels] fp32.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) causal_conv_kernel(float* __restrict__ out, const float* __restrict__ u, int ld, int offset, const float* __restrict__ w,
+                                                          const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
+                                                          const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                                          const int* __restrict__ seq_of_token, int channels, int taps) {
+  pdl_begin();
+  const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= channels) return;
+  const int s = seq_of_token[t];
+  const int j = t - q_start[s];
+  const float* st = state + (long long)state_slots[s] * slot_stride;
+  float acc = bias ? bias[c] : 0.f;
+  for (int l = taps - 1; l >= 0; --l) {  // the oldest input first
+    const int jj = j - l;
+    const float v = jj >= 0 ? u[(size_t)(t - l) * ld + offset + c] : st[(size_t)(taps - 1 + jj) * channels + c];
+    acc = fmaf(w[(size_t)c * taps + taps - 1 - l], v, acc);
+  }
+  out[(size_t)t * channels + c] = silu_f(acc);
+}
+
+// The state after the step: the last taps - 1 inputs of each request.  One thread per (request,
+// channel) moves its own column: entry i becomes input number count - (taps - 1) + i of the step,
+// or, where that is before the step's first token, the old entry i + count (always a later entry
+// than the one being written, so ascending order reads every old value before it is overwritten).
+__global__ void __launch_bounds__(256) conv_state_kernel(float* __restrict__ state, long long slot_stride, const float* __restrict__ u, int ld, int offset,
+                                                         const int* __restrict__ q_start, const int* __restrict__ state_slots, int channels, int taps) {
+  pdl_begin();
+  const int s = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+  if (c >= channels) return;
+  const int t0 = q_start[s], count = q_start[s + 1] - t0;
+  float* st = state + (long long)state_slots[s] * slot_stride;
+  for (int i = 0; i < taps - 1; ++i) {
+    const int idx = count - (taps - 1) + i;
+    st[(size_t)i * channels + c] = idx >= 0 ? u[(size_t)(t0 + idx) * ld + offset + c] : st[(size_t)(i + count) * channels + c];
+  }
+}
+
+ALOFA_API int alofa_causal_conv(float* out, const float* u, int ld, int offset, const float* w, const float* bias, float* state, long long slot_stride,
+                                const int* q_start, const int* state_slots, const int* seq_of_token, int n_tokens, int n_seqs, int channels, int taps,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (channels <= 0 || taps <= 0) return ALOFA_ERR_ARGUMENT;
+  launch_dep(causal_conv_kernel, dim3(n_tokens, (channels + 255) / 256), 256, 0, stream, out, u, ld, offset, w, bias, (const float*)state, slot_stride, q_start,
+             state_slots, seq_of_token, channels, taps);
+  if (taps > 1)
+    launch_dep(conv_state_kernel, dim3(n_seqs, (channels + 255) / 256), 256, 0, stream, state, slot_stride, u, ld, offset, q_start, state_slots, channels, taps);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The recurrence.  One block takes one (request, head) and a range of value channels and walks the
+// request's tokens of this step in order.  A thread holds R consecutive key channels of one value
+// channel of the state in registers (the state lies in memory as [head][value channel][key
+// channel]); the NS threads that share a value channel are neighbours in a warp and add their
+// shares of y in butterfly order.  Keys, queries, decays and values of TC tokens at a time are
+// staged in shared memory, where the decays are made: softplus, exponentials and the logarithm of
+// the sigmoid are the precise fp32 library functions.
+//
+//   mode 0 (one decay per head and token): dt = softplus(dec[t, h] + dt_bias[h]),
+//          a = exp(-exp(A_log[h]) * dt), k = dt * b[t, g, :], q = c[t, g, :], y += D[h] * v
+//   mode 1 (one decay per key channel):    a[n] = exp(log_sigmoid(dec[t, h, n]) * tau_inv),
+//          k = b[t, h, :], q = c[t, h, :] * q_scale
+// with g = h / (H / G) the group of head h.
+// ---------------------------------------------------------------------------
+struct ScanArgs {
+  float* y;            // [T, H * P]
+  const float* v; int ldv, v_off;      // values:  v[t * ldv + v_off + h * P + p]
+  const float* b; int ldb, b_off;      // keys:    b[t * ldb + b_off + g * N + n]
+  const float* c; int ldc, c_off;      // queries: c[t * ldc + c_off + g * N + n]
+  const float* dec; int ldd, d_off;    // decay inputs: mode 0 [t, h], mode 1 [t, h * N + n]
+  const float* dt_bias; const float* A_log; const float* D;
+  float tau_inv, q_scale;
+  float* state; long long slot_stride;  // state of slot s at state + s * slot_stride, [H][P][N]
+  const int* q_start; const int* state_slots;
+  int H, G, N, P, mode, NS, PC;
+};
+
+constexpr int SCAN_TC = 16;
+
+template <int R>
+__global__ void __launch_bounds__(512) linear_scan_kernel(const ScanArgs a) {
+  extern __shared__ float scan_smem[];
+  const int N = a.N, P = a.P, NS = a.NS, PC = a.PC;
+  const int NP = N + (N >> 5) + 1;  // padded rows: threads R apart do not meet in one bank
+  float* ks = scan_smem;                  // [TC][NP]
+  float* qs = ks + SCAN_TC * NP;          // [TC][NP]
+  float* as = qs + SCAN_TC * NP;          // [TC][NP] (mode 1) or [TC] (mode 0)
+  float* vs = as + (a.mode ? SCAN_TC * NP : SCAN_TC);  // [TC][PC]
+  pdl_begin();
+  const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * PC;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int pl = tid / NS, ns = tid - pl * NS;
+  const int p = p0 + pl;
+  const bool active = pl < PC && p < P;
+  const int g = h / (a.H / a.G);
+  const int t0 = a.q_start[s], t1 = a.q_start[s + 1];
+  float* S = a.state + (long long)a.state_slots[s] * a.slot_stride + ((size_t)h * P + (active ? p : 0)) * N;
+  const int n0 = ns * R;
+  float st[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) st[i] = (active && n0 + i < N) ? S[n0 + i] : 0.f;
+  const float dskip = (a.mode == 0 && a.D) ? a.D[h] : 0.f;
+  const float rate = a.mode == 0 ? expf(a.A_log[h]) : 0.f;
+  const float dtb = (a.mode == 0 && a.dt_bias) ? a.dt_bias[h] : 0.f;
+  for (int c0 = t0; c0 < t1; c0 += SCAN_TC) {
+    const int live = min(SCAN_TC, t1 - c0);
+    __syncthreads();
+    if (a.mode == 0) {
+      for (int tt = tid; tt < live; tt += nthreads) as[tt] = softplus_f(a.dec[(size_t)(c0 + tt) * a.ldd + a.d_off + h] + dtb);
+      __syncthreads();
+    }
+    for (int e = tid; e < live * N; e += nthreads) {
+      const int tt = e / N, n = e - tt * N;
+      const size_t t = c0 + tt;
+      const int at = tt * NP + n + (n >> 5);
+      const float kv = a.b[t * a.ldb + a.b_off + g * N + n];
+      qs[at] = a.c[t * a.ldc + a.c_off + g * N + n] * a.q_scale;
+      if (a.mode == 0) {
+        ks[at] = as[tt] * kv;
+      } else {
+        ks[at] = kv;
+        const float z = a.dec[t * a.ldd + a.d_off + h * N + n];
+        as[at] = expf(-softplus_f(-z) * a.tau_inv);  // sigmoid(z)^(1/tau) through its logarithm
+      }
+    }
+    for (int e = tid; e < live * PC; e += nthreads) {
+      const int tt = e / PC, q = e - tt * PC;
+      vs[e] = p0 + q < P ? a.v[(size_t)(c0 + tt) * a.ldv + a.v_off + h * P + p0 + q] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < live; ++tt) {
+      const float xv = pl < PC ? vs[tt * PC + pl] : 0.f;
+      const float* kr = ks + tt * NP;
+      const float* qr = qs + tt * NP;
+      float acc = 0.f;
+      if (a.mode == 0) {
+        const float dec = expf(-rate * as[tt]);
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int n = n0 + i, at = n + (n >> 5);
+          if (n < N) {
+            st[i] = fmaf(dec, st[i], kr[at] * xv);
+            acc = fmaf(st[i], qr[at], acc);
+          }
+        }
+      } else {
+        const float* ar = as + tt * NP;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          const int n = n0 + i, at = n + (n >> 5);
+          if (n < N) {
+            st[i] = fmaf(ar[at], st[i], kr[at] * xv);
+            acc = fmaf(st[i], qr[at], acc);
+          }
+        }
+      }
+      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (active && ns == 0) a.y[(size_t)(c0 + tt) * a.H * P + h * P + p] = acc + dskip * xv;
+    }
+  }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+      if (n0 + i < N) S[n0 + i] = st[i];
+  }
+}
+
+template <int R>
+static int linear_scan_launch(const ScanArgs& a, int n_seqs, int threads, size_t smem, cudaStream_t stream) {
+  static size_t set = 48 * 1024;
+  if (smem > set) {
+    if (cudaFuncSetAttribute(linear_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    set = smem;
+  }
+  launch_dep(linear_scan_kernel<R>, dim3(a.H, n_seqs, (a.P + a.PC - 1) / a.PC), threads, smem, stream, a);
+  return launch_status();
+}
+
+// `spread`: how many blocks the launch should have at least, if the value channels allow it (a
+// prompt of one request has few (request, head) pairs; its value channels are dealt to more blocks).
+ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, const float* b, int ldb, int b_off, const float* c, int ldc, int c_off,
+                                const float* dec, int ldd, int d_off, const float* dt_bias, const float* A_log, const float* D, float tau_inv, float q_scale,
+                                float* state, long long slot_stride, const int* q_start, const int* state_slots, int n_seqs, int H, int G, int N, int P,
+                                int mode, int spread, cudaStream_t stream) {
+  if (n_seqs <= 0) return ALOFA_OK;
+  if (H <= 0 || G <= 0 || H % G || N <= 0 || N > 1024 || P <= 0 || (mode == 0 && !A_log)) return ALOFA_ERR_ARGUMENT;
+  const int R = N <= 256 ? 8 : (N <= 512 ? 16 : 32);
+  int NS = 1;
+  while (NS * R < N) NS *= 2;
+  int PC = 512 / NS;  // value channels per block
+  if (PC > P) PC = P;
+  while (PC > 8 && (long long)H * n_seqs * ((P + PC - 1) / PC) < spread) PC = (PC + 1) / 2;
+  const int threads = (PC * NS + 31) / 32 * 32;
+  ScanArgs a = {y, v, ldv, v_off, b, ldb, b_off, c, ldc, c_off, dec, ldd, d_off, dt_bias, A_log, D, tau_inv, q_scale, state, slot_stride, q_start, state_slots,
+                H, G, N, P, mode, NS, PC};
+  const int NP = N + (N >> 5) + 1;
+  const size_t smem = ((size_t)SCAN_TC * NP * (mode ? 3 : 2) + (mode ? 0 : SCAN_TC) + (size_t)SCAN_TC * PC) * sizeof(float);
+  if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
+  if (R == 8) return linear_scan_launch<8>(a, n_seqs, threads, smem, stream);
+  if (R == 16) return linear_scan_launch<16>(a, n_seqs, threads, smem, stream);
+  return linear_scan_launch<32>(a, n_seqs, threads, smem, stream);
+}
+
+// ---------------------------------------------------------------------------
+// The norm such a mixer ends with: rows y [T, width] in `groups` equal parts, each part divided by
+// its own root mean square (eps inside the root), times w[c % wlen], and a gate silu(g[t, c]) that
+// multiplies either before the norm (gate_first: the gated values are what is normed) or after it.
+// One block per token, a warp per part in turn.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ gate, int ldg,
+                                                               int g_off, const float* __restrict__ w, int wlen, int width, int groups, float eps,
+                                                               int gate_first) {
+  pdl_begin();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = width / groups;
+  const float* yr = y + (size_t)t * width;
+  const float* gr = gate ? gate + (size_t)t * ldg + g_off : nullptr;
+  for (int grp = warp; grp < groups; grp += 8) {
+    const int lo = grp * part;
+    float ss = 0.f;
+    for (int c = lo + lane; c < lo + part; c += 32) {
+      float v = yr[c];
+      if (gr && gate_first) v *= silu_f(gr[c]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)part + eps);
+    for (int c = lo + lane; c < lo + part; c += 32) {
+      float v = yr[c];
+      if (gr && gate_first) v *= silu_f(gr[c]);
+      v = v * r * w[c % wlen];
+      if (gr && !gate_first) v *= silu_f(gr[c]);
+      out[(size_t)t * width + c] = from_f<TO>(v);
+    }
+  }
+}
+
+ALOFA_API int alofa_gated_group_norm(void* out, const float* y, const float* gate, int ldg, int g_off, const float* w, int wlen, int n_tokens, int width,
+                                     int groups, float eps, int gate_first, int out_bf16, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (groups <= 0 || width % groups || wlen <= 0) return ALOFA_ERR_ARGUMENT;
+  if (out_bf16) launch_dep(gated_group_norm_kernel<bf16>, n_tokens, 256, 0, stream, (bf16*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
+  else launch_dep(gated_group_norm_kernel<float>, n_tokens, 256, 0, stream, (float*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// h += scale * (rmsnorm(ya) * wa + rmsnorm(yb) * wb): the outputs of branches that ran side by
+// side, each normed over the model width with its own plain weight, into the fp32 residual stream
+// (yb may be absent).  One block per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ ya, const float* __restrict__ wa,
+                                                              const float* __restrict__ yb, const float* __restrict__ wb, int hidden, float eps,
+                                                              float scale) {
+  __shared__ float scratch[32];
+  pdl_begin();
+  const size_t row = (size_t)blockIdx.x * hidden;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += 256) {
+    const float va = ya[row + c];
+    sa = fmaf(va, va, sa);
+    if (yb) {
+      const float vb = yb[row + c];
+      sb = fmaf(vb, vb, sb);
+    }
+  }
+  sa = block_sum(sa, scratch);
+  const float ra = 1.0f / sqrtf(sa / (float)hidden + eps);
+  float rb = 0.f;
+  if (yb) {
+    sb = block_sum(sb, scratch);
+    rb = 1.0f / sqrtf(sb / (float)hidden + eps);
+  }
+  for (int c = threadIdx.x; c < hidden; c += 256) {
+    float v = ya[row + c] * ra * wa[c];
+    if (yb) v += yb[row + c] * rb * wb[c];
+    h[row + c] += scale * v;
+  }
+}
+
+ALOFA_API int alofa_branch_norm_add(float* h, const float* ya, const float* wa, const float* yb, const float* wb, int rows, int hidden, float eps, float scale,
+                                    cudaStream_t stream) {
+  if (rows <= 0) return ALOFA_OK;
+  launch_dep(branch_norm_add_kernel, rows, 256, 0, stream, h, ya, wa, yb, wb, hidden, eps, scale);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Queries, keys and values of softmax attention without rotation, from the fp32 sums of one stacked
+// projection [q: H * d | k: G * d | v: G * dv]:  q and k divided by their root mean square over
+// d per head (qk_norm; no weight), q times 1 + coef * ln(floor((p + 1) / every) + 1) at position p
+// (coef != 0), q to its own buffer, k and v to the token's cache slot.  A warp per (token, head).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, const float* __restrict__ qkv,
+                                                          const int* __restrict__ positions, const int* __restrict__ slot_map, int H, int G, int d, int dv,
+                                                          int qk_norm, float eps, float coef, int every, int n_tokens) {
+  pdl_begin();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = H + 2 * G;
+  const long long unit = (long long)blockIdx.x * 8 + warp;
+  if (unit >= (long long)n_tokens * per) return;
+  const int t = (int)(unit / per), u = (int)(unit - (long long)t * per);
+  const int ld = H * d + G * d + G * dv;
+  const float* row = qkv + (size_t)t * ld;
+  if (u < H + G) {
+    const float* x = row + (size_t)u * d;
+    float mul = 1.f;
+    if (qk_norm) {
+      float ss = 0.f;
+      for (int c = lane; c < d; c += 32) ss = fmaf(x[c], x[c], ss);
+      ss = warp_sum(ss);
+      mul = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    T* to;
+    if (u < H) {
+      if (coef != 0.f) mul *= 1.0f + coef * logf((float)((positions[t] + 1) / every) + 1.0f);
+      to = q_out + ((size_t)t * H + u) * d;
+    } else {
+      to = k_cache + ((size_t)slot_map[t] * G + (u - H)) * d;
+    }
+    for (int c = lane; c < d; c += 32) to[c] = from_f<T>(x[c] * mul);
+  } else {
+    const int gi = u - H - G;
+    const float* x = row + (size_t)(H + G) * d + (size_t)gi * dv;
+    T* to = v_cache + ((size_t)slot_map[t] * G + gi) * dv;
+    for (int c = lane; c < dv; c += 32) to[c] = from_f<T>(x[c]);
+  }
+}
+
+ALOFA_API int alofa_qkv_prepare(void* q_out, void* k_cache, void* v_cache, const float* qkv, const int* positions, const int* slot_map, int n_tokens, int H, int G,
+                                int d, int dv, int qk_norm, float eps, float coef, int every, int is_bf16, cudaStream_t stream) {
+  if (n_tokens <= 0) return ALOFA_OK;
+  if (H <= 0 || G <= 0 || d <= 0 || dv <= 0 || (coef != 0.f && every <= 0)) return ALOFA_ERR_ARGUMENT;
+  const long long units = (long long)n_tokens * (H + 2 * G);
+  const unsigned blocks = (unsigned)((units + 7) / 8);
+  if (is_bf16)
+    launch_dep(qkv_prepare_kernel<bf16>, blocks, 256, 0, stream, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps, coef,
+               every, n_tokens);
+  else
+    launch_dep(qkv_prepare_kernel<float>, blocks, 256, 0, stream, (float*)q_out, (float*)k_cache, (float*)v_cache, qkv, positions, slot_map, H, G, d, dv, qk_norm, eps,
+               coef, every, n_tokens);
+  return launch_status();
+}

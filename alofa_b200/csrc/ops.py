@@ -41,7 +41,7 @@ def _generic():
             "alofa_rmsnorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
             "alofa_gemm_generic": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
             "alofa_rope_store": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+            "alofa_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -261,18 +261,23 @@ def rope_store(q_out, k_cache, v_cache, qkv, cos_sin, positions, slot_map, nh, n
     )
 
 
-def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale) -> None:
-    """Causal GQA over the paged cache, any head size up to 256."""
+def paged_attention_generic(out, q, k_cache, v_cache, positions, seq_of_token, block_table, page_size, nh, nkv, hd, window, scale, softcap: float = 0.0, vd=None) -> None:
+    """Causal grouped-query attention over the paged cache for every size and
+    both dtypes; fp32 scores and softmax.  ``softcap`` > 0 bounds the scaled
+    scores by ``softcap * tanh(score / softcap)``; ``vd`` is the values' head
+    size when it differs from the keys' ``hd``."""
     n = q.shape[0]
+    vd = hd if vd is None else vd
     dt = q.dtype
+    if tuple(k_cache.shape[1:]) != (nkv, hd) or tuple(v_cache.shape[1:]) != (nkv, vd) or tuple(q.shape) != (n, nh * hd) or tuple(out.shape) != (n, nh * vd):
+        raise AlofaError("invalid_argument", "attention sizes disagree", f"q={tuple(q.shape)} out={tuple(out.shape)} k={tuple(k_cache.shape)} v={tuple(v_cache.shape)}")
     _done(
         _generic().alofa_paged_attention_generic(
             _dev(out, "out", dt), _dev(q, "q"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt),
-            _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
-            _dev(block_table, "block_table", torch.int32), block_table.shape[1], page_size, n, nh, nkv, hd,
-            int(window or 0), float(scale), _is_bf16(q, "q"), _stream(),
+            _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32), _dev(block_table, "block_table", torch.int32),
+            block_table.shape[1], page_size, n, nh, nkv, hd, vd, int(window or 0), float(scale), float(softcap or 0.0), _is_bf16(q, "q"), _stream(),
         ),
-        "paged_attention_generic", f"hd={hd} nh={nh} nkv={nkv}",
+        "paged_attention_generic", f"heads={nh} kv_heads={nkv} head_dim={hd} v_head_dim={vd}",
     )
 
 
@@ -560,10 +565,11 @@ def _latent():
             "alofa_sandwich_norm": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _I, _P],
             "alofa_concat_rows": [_P, _P, _P, _I, _I, _I, _P],
             "alofa_moe_route": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-            "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_moe_router": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _F, _P],
             "alofa_moe_sort": [_P, _P, _P, _I, _I, _I, _I, _P],
             "alofa_moe_scatter": [_P, _P, _P, _P, _I, _I, _I, _I, _P],
-            "alofa_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+            "alofa_moe_combine": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _P],
+            "alofa_gate_up": [_P, _P, _L, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
@@ -735,16 +741,20 @@ def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = F
     )
 
 
-def moe_router(choice, weight, gate, x, wr, experts: int, top: int, softmax: bool = False, renormalize: bool = False) -> None:
+def moe_router(choice, weight, gate, x, wr, experts: int, top: int, softmax: bool = False, renormalize: bool = False, correction=None,
+               renorm_eps: float = 0.0) -> None:
     """:func:`moe_route` with the router's product in the same kernel: ``x``
     [T, hidden] in the compute dtype, ``wr`` fp32 [experts (+1 with ``gate``),
-    hidden]; logits and scores are fp32."""
+    hidden]; logits and scores are fp32.  ``correction`` (fp32 [experts]) is
+    added to the scores for the choice only, the weights stay the scores;
+    ``renorm_eps`` is added to the sum that ``renormalize`` divides by."""
     i32, f32 = torch.int32, torch.float32
-    if wr.shape != (experts + (1 if gate is not None else 0), x.shape[1]):
+    if wr.shape != (experts + (1 if gate is not None else 0), x.shape[1]) or (correction is not None and correction.shape[0] != experts):
         raise AlofaError("invalid_argument", "router sizes disagree", f"wr={tuple(wr.shape)} x={tuple(x.shape)} experts={experts}")
     _done(
         _latent().alofa_moe_router(_dev(choice, "choice", i32), _dev(weight, "weight", f32), _dev(gate, "gate", f32) if gate is not None else None, _dev(x, "x"),
-                                   _dev(wr, "wr", f32), x.shape[0], experts, top, x.shape[1], 1 if softmax else 0, 1 if renormalize else 0, _is_bf16(x, "x"), _stream()),
+                                   _dev(wr, "wr", f32), x.shape[0], experts, top, x.shape[1], 1 if softmax else 0, 1 if renormalize else 0, _is_bf16(x, "x"),
+                                   _dev(correction, "correction", f32) if correction is not None else None, float(renorm_eps), _stream()),
         "moe_router", f"experts={experts} top={top}",
     )
 
@@ -763,15 +773,27 @@ def moe_scatter(xs, x, weight, dest, top: int) -> None:
                                       _dev(dest, "dest", torch.int32), dest.numel(), top, x.shape[1], _is_bf16(x, "x"), _stream()), "moe_scatter")
 
 
-def moe_combine(y, ys, dest, weight, shared, gate, top: int) -> None:
-    """y[t] = sum_k (weight[t, k] *) ys[dest[t, k]] + (gate[t] *) shared[t], fp32."""
+def moe_combine(y, ys, dest, weight, shared, gate, top: int, x=None, add: bool = False) -> None:
+    """y[t] = sum_k (weight[t, k] *) ys[dest[t, k]] + (gate[t] *) shared[t], fp32;
+    a pair whose ``dest`` is negative (an expert that is the identity) takes
+    the token's own input ``x[t]`` instead of a row; ``add``: y += the sum."""
     f32 = torch.float32
     _done(
         _latent().alofa_moe_combine(_dev(y, "y", f32), _dev(ys, "ys", f32), _dev(dest, "dest", torch.int32), _dev(weight, "weight", f32) if weight is not None else None,
                                     _dev(shared, "shared", f32) if shared is not None else None, _dev(gate, "gate", f32) if gate is not None else None,
-                                    y.shape[0], top, y.shape[1], _stream()),
+                                    y.shape[0], top, y.shape[1], _dev(x, "x") if x is not None else None, _is_bf16(x, "x") if x is not None else 0,
+                                    1 if add else 0, _stream()),
         "moe_combine",
     )
+
+
+def gate_up(mid, gu) -> None:
+    """mid[r, c] = silu(gu[r, c]) * gu[r, ff + c] for rows of fp32 sums that
+    hold gate and up side by side; ``mid`` in its own dtype."""
+    rows, ff = mid.shape
+    if tuple(gu.shape) != (rows, 2 * ff):
+        raise AlofaError("invalid_argument", "gate_up sizes disagree", f"mid={tuple(mid.shape)} gu={tuple(gu.shape)}")
+    _done(_latent().alofa_gate_up(_dev(mid, "mid"), _dev(gu, "gu", torch.float32), rows, ff, _is_bf16(mid, "mid"), _stream()), "gate_up")
 
 
 def latent_attention_bf16_supported(kv_rank: int, rot: int) -> bool:
@@ -823,3 +845,152 @@ def latent_attention_bf16(out, qa, cache_rows, sink, q_start, kv_len, block_tabl
     )
     if splits > 1:
         count_launches(1)
+
+
+# -- mixers with a state of fixed size, and what stands around them --------------------------------
+def _recurrent():
+    lib = _libs.get("recurrent")
+    if lib is None:
+        lib = load_library("alofa_recurrent", ["kernels/recurrent.cu"])
+        sigs = {
+            "alofa_embed_scaled": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
+            "alofa_add_rows": [_P, _P, _L, _P],
+            "alofa_causal_conv": [_P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
+            "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
+            "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
+            "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        }
+        for name, args in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype = _I
+            fn.argtypes = args
+        _libs["recurrent"] = lib
+    return lib
+
+
+def embed_scaled(out, table, ids, positions, scale: float, freq=None, status=None, src=None, fed=None) -> None:
+    """out[t] = table[ids[t]] * scale (+ the sinusoidal position vector of
+    ``positions[t]``: entry 2i sin(p freq[i]), entry 2i + 1 cos(p freq[i]));
+    out fp32 [T, H], freq fp32 [ceil(H / 2)] or None.  ``src`` / ``fed`` as in
+    :func:`embed_gather`."""
+    n, hidden = out.shape
+    if freq is not None and freq.shape[0] != (hidden + 1) // 2:
+        raise AlofaError("invalid_argument", "embed_scaled sizes disagree", f"out={tuple(out.shape)} freq={tuple(freq.shape)}")
+    i32 = torch.int32
+    _done(
+        _recurrent().alofa_embed_scaled(
+            _dev(out, "out", torch.float32), _dev(table, "table"), _dev(ids, "ids", i32), _dev(src, "src", i32) if src is not None else None,
+            _dev(fed, "fed", i32) if src is not None else None, _dev(positions, "positions", i32), _dev(freq, "freq", torch.float32) if freq is not None else None,
+            n, hidden, table.shape[0], float(scale), _is_bf16(table, "table"), _dev(status, "status", i32) if status is not None else None, _stream(),
+        ),
+        "embed_scaled",
+    )
+
+
+def add_rows(out, x) -> None:
+    """out += x (fp32, same shape)."""
+    if out.shape != x.shape:
+        raise AlofaError("invalid_argument", "add_rows sizes disagree", f"out={tuple(out.shape)} x={tuple(x.shape)}")
+    _done(_recurrent().alofa_add_rows(_dev(out, "out", torch.float32), _dev(x, "x", torch.float32), out.numel(), _stream()), "add_rows")
+
+
+def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_of_token, n_seqs: int) -> None:
+    """out [T, C] = silu(bias + causal convolution per channel) of the columns
+    ``offset .. offset + C`` of u [T, ld] (fp32), w [C, taps] fp32 with the
+    token's own tap last; ``state`` [slots, >= (taps - 1) * C] fp32 holds each
+    request's last taps - 1 inputs and is brought up to date."""
+    n, channels = out.shape
+    taps = w.shape[1]
+    f32, i32 = torch.float32, torch.int32
+    if w.shape[0] != channels or u.shape[0] != n or offset + channels > u.shape[1] or state.stride(0) < (taps - 1) * channels:
+        raise AlofaError("invalid_argument", "causal_conv sizes disagree", f"out={tuple(out.shape)} u={tuple(u.shape)} w={tuple(w.shape)}")
+    if state.dtype != f32 or not state.is_cuda or state.stride(-1) != 1:
+        raise AlofaError("invalid_argument", "causal_conv needs an fp32 state on the device")
+    _done(
+        _recurrent().alofa_causal_conv(
+            _dev(out, "out", f32), _dev(u, "u", f32), u.shape[1], offset, _dev(w, "w", f32), _dev(bias, "bias", f32) if bias is not None else None,
+            state.data_ptr(), state.stride(0), _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), _dev(seq_of_token, "seq_of_token", i32),
+            n, n_seqs, channels, taps, _stream(),
+        ),
+        "causal_conv", f"channels={channels} taps={taps}",
+    )
+    if taps > 1:
+        count_launches(1)  # the kernel that moves the state on
+
+
+def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int, state, q_start, state_slots, n_seqs: int, heads: int, groups: int, n: int, p: int,
+                mode: int, dt_bias=None, a_log=None, d_skip=None, tau: float = 1.0, q_scale: float = 1.0, spread: int = 0) -> None:
+    """The recurrence ``S_t = diag(a_t) S_(t-1) + k_t v_t^T, y_t = S_t^T q_t``
+    per head over each request's tokens of the step in order, all fp32; the
+    state [slots, >= heads * p * n] (per head [p][n]) is read and left up to
+    date.  ``v``, ``b`` (keys), ``c`` (queries), ``dec`` are fp32 matrices of
+    one row per token, read at the given column offsets.  ``mode`` 0: one
+    decay per head, ``dt = softplus(dec[t, h] + dt_bias[h])``, ``a =
+    exp(-exp(a_log[h]) dt)``, keys times dt, ``y += d_skip[h] v``, keys and
+    queries shared by the heads of a group.  ``mode`` 1: one decay per key
+    channel, ``a = sigmoid(dec[t, h, :]) ** (1 / tau)``, queries times
+    ``q_scale``."""
+    f32, i32 = torch.float32, torch.int32
+    rows = y.shape[0]
+    if tuple(y.shape) != (rows, heads * p) or state.stride(0) < heads * p * n or state.dtype != f32 or not state.is_cuda:
+        raise AlofaError("invalid_argument", "linear_scan sizes disagree", f"y={tuple(y.shape)} state={tuple(state.shape)} heads={heads} n={n} p={p}")
+    for t_, name in ((v, "v"), (b, "b"), (c, "c"), (dec, "dec")):
+        if t_.shape[0] != rows or t_.dtype != f32 or t_.dim() != 2:
+            raise AlofaError("invalid_argument", "linear_scan operand must be fp32 with one row per token", name)
+    opt = lambda t_, name: _dev(t_, name, f32) if t_ is not None else None
+    _done(
+        _recurrent().alofa_linear_scan(
+            _dev(y, "y", f32), _dev(v, "v"), v.shape[1], v_off, _dev(b, "b"), b.shape[1], b_off, _dev(c, "c"), c.shape[1], c_off, _dev(dec, "dec"), dec.shape[1], d_off,
+            opt(dt_bias, "dt_bias"), opt(a_log, "a_log"), opt(d_skip, "d_skip"), 1.0 / float(tau), float(q_scale), state.data_ptr(), state.stride(0),
+            _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, heads, groups, n, p, mode, spread, _stream(),
+        ),
+        "linear_scan", f"heads={heads} groups={groups} n={n} p={p} mode={mode}",
+    )
+
+
+def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_first: bool) -> None:
+    """out = rows of y [T, width] normed in ``groups`` equal parts (each by
+    its own root mean square), times ``w[c % len(w)]``, with the gate
+    ``silu(gate[t, g_off + c])`` multiplied in before the norm
+    (``gate_first``) or after it; fp32 in, out in its own dtype."""
+    n, width = y.shape
+    f32 = torch.float32
+    if tuple(out.shape) != (n, width) or (gate is not None and (gate.shape[0] != n or g_off + width > gate.shape[1])):
+        raise AlofaError("invalid_argument", "gated_group_norm sizes disagree", f"y={tuple(y.shape)} out={tuple(out.shape)}")
+    _done(
+        _recurrent().alofa_gated_group_norm(_dev(out, "out"), _dev(y, "y", f32), _dev(gate, "gate", f32) if gate is not None else None,
+                                            gate.shape[1] if gate is not None else 0, g_off, _dev(w, "w", f32), w.shape[0], n, width, groups, float(eps),
+                                            1 if gate_first else 0, _is_bf16(out, "out"), _stream()),
+        "gated_group_norm", f"width={width} groups={groups}",
+    )
+
+
+def branch_norm_add(h, ya, wa, yb, wb, eps: float, scale: float) -> None:
+    """h += scale * (rmsnorm(ya) * wa + rmsnorm(yb) * wb), all fp32 [T, hidden]; ``yb`` may be None."""
+    f32 = torch.float32
+    rows, hidden = h.shape
+    if tuple(ya.shape) != (rows, hidden) or (yb is not None and tuple(yb.shape) != (rows, hidden)):
+        raise AlofaError("invalid_argument", "branch_norm_add sizes disagree", f"h={tuple(h.shape)} ya={tuple(ya.shape)}")
+    _done(
+        _recurrent().alofa_branch_norm_add(_dev(h, "h", f32), _dev(ya, "ya", f32), _dev(wa, "wa", f32), _dev(yb, "yb", f32) if yb is not None else None,
+                                           _dev(wb, "wb", f32) if yb is not None else None, rows, hidden, float(eps), float(scale), _stream()),
+        "branch_norm_add",
+    )
+
+
+def qkv_prepare(q_out, k_cache, v_cache, qkv, positions, slot_map, heads: int, kv_heads: int, d: int, dv: int, qk_norm: bool, eps: float, coef: float, every: int) -> None:
+    """From the fp32 sums of a stacked projection [q | k | v]: q and k divided
+    by their root mean square per head (``qk_norm``), q times ``1 + coef *
+    ln(floor((p + 1) / every) + 1)`` at position p, q to ``q_out``, k and v to
+    the tokens' cache slots; out tensors in the compute dtype."""
+    n = qkv.shape[0]
+    dt = q_out.dtype
+    if qkv.shape[1] != heads * d + kv_heads * (d + dv) or tuple(q_out.shape) != (n, heads * d) or tuple(k_cache.shape[1:]) != (kv_heads, d) or tuple(v_cache.shape[1:]) != (kv_heads, dv):
+        raise AlofaError("invalid_argument", "qkv_prepare sizes disagree", f"qkv={tuple(qkv.shape)} q={tuple(q_out.shape)} k={tuple(k_cache.shape)} v={tuple(v_cache.shape)}")
+    _done(
+        _recurrent().alofa_qkv_prepare(_dev(q_out, "q_out"), _dev(k_cache, "k_cache", dt), _dev(v_cache, "v_cache", dt), _dev(qkv, "qkv", torch.float32),
+                                       _dev(positions, "positions", torch.int32), _dev(slot_map, "slot_map", torch.int32), n, heads, kv_heads, d, dv,
+                                       1 if qk_norm else 0, float(eps), float(coef), int(every), _is_bf16(q_out, "q_out"), _stream()),
+        "qkv_prepare",
+    )

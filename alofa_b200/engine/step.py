@@ -26,7 +26,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, GroupSpec
-from ..cache.storage import CacheStorage, group_windows
+from ..cache.storage import CacheStorage, flat_specs, group_windows
 from ..csrc import ops
 from ..errors import AlofaError
 from ..parts.base import PagedKV, PagedRows
@@ -78,7 +78,7 @@ class StepRunner:
         self.group_specs = [GroupSpec(block_size, n, w) for n, w in zip(num_pages, windows)]
         self.manager = CacheManager(self.group_specs, max_requests, self.max_tokens)
         self.storage = CacheStorage(plan, self.group_specs, max_requests, self.rt.dtype, self.rt.device)
-        self.has_paged = any(isinstance(s, (PagedKV, PagedRows)) for s in plan.values())
+        self.has_paged = any(isinstance(s, (PagedKV, PagedRows)) for s in flat_specs(plan))
         mb = self.manager.max_blocks
         self._group_shapes = [GroupView(block_size, g.window or 0, mb) for g in self.group_specs]
         words = Layout.make(max_step_tokens, max_requests, max_step_tokens, self._group_shapes).total

@@ -9,5 +9,5 @@ from .base import (  # noqa: F401
     build_part,
     register_part,
 )
-from . import attention, block, embedding, feed_forward, latent_attention, norm, position, routed  # noqa: F401,E402
+from . import attention, block, embedding, feed_forward, latent_attention, norm, normed_attention, position, recurrent, routed, side_by_side  # noqa: F401,E402
 from .model import Model, expected_tensors  # noqa: F401,E402

@@ -14,7 +14,9 @@ Interfaces (``ctx`` is the step's :class:`~alofa_b200.engine.context.StepContext
 * norm: ``forward(ctx, h, rows=None) -> x`` in the compute dtype;
 * position: ``rotary_table()`` (cos/sin table and rotary_dim, or None) and
   ``apply(ctx, q, k)`` for encodings that are not rotary;
-* mixer: ``cache_spec()`` (PagedKV, PagedRows, SlotState or None) and
+* mixer: ``cache_spec()`` (PagedKV, PagedRows, SlotState, None, or a tuple of
+  these for a mixer made of several that run side by side: its ``cache`` is
+  then the tuple of their caches) and
   ``forward(ctx, x, h, cache, writes)`` which adds its output into ``h``;
 * feed_forward: ``forward(ctx, x, h)`` which adds its output into ``h``;
 * block: ``cache_spec()`` and ``forward(ctx, h, cache, writes)``;
@@ -38,7 +40,8 @@ _REGISTRY: dict = {f: {} for f in FAMILIES}
 class TensorSpec:
     """A tensor a part expects under its name: shape, the law random weights
     are drawn from ("normal": N(0, 0.02); "ones": 1 + N(0, 0.01)), and whether
-    the file may leave it out."""
+    the file may leave it out.  A negative entry of ``shape`` is a size that
+    the file decides; random weights use its magnitude."""
 
     shape: tuple
     init: str = "normal"
@@ -47,11 +50,13 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class PagedKV:
-    """A mixer's need of a paged key/value cache: ``window`` None = all keys."""
+    """A mixer's need of a paged key/value cache: ``window`` None = all keys;
+    ``v_head_dim`` None = values as wide as keys."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -5,6 +5,10 @@
 feed-forward may be absent.  ``embedding_mix_in``: no sublayers at all, ``h =
 W [h; e]`` with ``e`` the embedding output of the step's tokens.
 
+``parallel_residual``: one norm whose output both sublayers read,
+``x = norm(h); h += mixer(x) + feed_forward(x)`` (the feed-forward may be
+absent).  ``embedding_add``: no sublayers, ``h += e``.
+
 ``prenorm_residual``: ``h += mixer(norm_a(h)); h += feed_forward(norm_b(h))``
 (src/alofa/model/arch/qwen.mojo:1367-1372, 1418-1510).  The residual stream
 ``h`` is fp32; the parts add into it."""
@@ -164,6 +168,72 @@ class EmbeddingMixIn(Part):
         self.linear(h, both, buf=ctx.buf)
 
 
+class ParallelResidual(Part):
+    """One norm, and the mixer and the feed-forward side by side on its
+    output; each adds what it makes into the fp32 stream."""
+
+    family = "block"
+    absorbs_pending = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.norm = build_part("norm", self.param("norm"), rt)
+        self.mixer = build_part("mixer", self.param("mixer"), rt)
+        ff = self.params.get("feed_forward")
+        self.feed_forward = build_part("feed_forward", ff, rt) if ff is not None else None
+
+    def parts(self):
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    def tensors(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.tensors())
+        return out
+
+    def load(self, state):
+        for part in self.parts():
+            part.load(state)
+
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self.parts())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def scratch_row_bytes(self) -> int:
+        return sum(getattr(part, "scratch_row_bytes", lambda: 0)() for part in self.parts())
+
+    def forward(self, ctx, h, cache, writes=True):
+        if not getattr(self.norm, "absorbs_pending", False):
+            ctx.flush_pending()
+        x = self.norm.forward(ctx, h)
+        # the feed-forward first: it adds into h itself, while the mixer's last product may leave sums for the next reader to add
+        if self.feed_forward is not None:
+            ctx.flush_pending()
+            self.feed_forward.forward(ctx, x, h)
+        self.mixer.forward(ctx, x, h, cache, writes)
+
+
+class EmbeddingAdd(Part):
+    """``h += e`` with ``e`` the embedding output of the step's tokens: what a
+    stretch of layers that runs several times gets before each further pass."""
+
+    family = "block"
+    graph_safe = True
+    needs_embedding_output = True
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, ctx, h, cache, writes=True):
+        ctx.flush_pending()
+        ops.add_rows(h, ctx.embedding_output)
+
+
 register_part("block", "prenorm_residual", PrenormResidual)
+register_part("block", "parallel_residual", ParallelResidual)
+register_part("block", "embedding_add", EmbeddingAdd)
 register_part("block", "sandwich_residual", SandwichResidual)
 register_part("block", "embedding_mix_in", EmbeddingMixIn)

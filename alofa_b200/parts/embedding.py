@@ -1,7 +1,11 @@
 """Token embedding and the output head.
 
 ``h[r] = embed[id_r]`` with ids outside the vocabulary refused
-(src/alofa/model/arch/qwen.mojo:1391-1413).  The head multiplies the normed
+(src/alofa/model/arch/qwen.mojo:1391-1413); with ``scale`` the row is
+multiplied by it, and with ``sinusoid_base`` a position vector is added whose
+entry 2i is ``sin(p * base^(-2i/hidden))`` and entry 2i + 1 the cosine of the
+same angle (frequencies made in float64 and rounded to fp32 once, the angle an
+fp32 product, precise sine and cosine).  The head multiplies the normed
 rows whose logits are wanted by ``lm_head.weight`` if the file has it, else by
 the embedding when the two are tied (qwen.mojo:1077-1089, 1512-1523); a tied
 head shares the embedding's memory."""
@@ -26,14 +30,25 @@ class TokenEmbedding(Part):
         self.hidden = int(self.param("hidden_size"))
         self.name = self.prefix + str(self.params.get("weight_name", "weight"))
         self.weight = None
+        self.scale = self.params.get("scale")
+        self.sinusoid_base = self.params.get("sinusoid_base")
+        self.freq = None
 
     def tensors(self):
         return {self.name: TensorSpec((self.vocab, self.hidden))}
 
     def load(self, state):
         self.weight = state[self.name]
+        if self.sinusoid_base is not None:
+            i = torch.arange((self.hidden + 1) // 2, dtype=torch.float64)
+            self.freq = (float(self.sinusoid_base) ** (-2.0 * i / self.hidden)).to(torch.float32).to(self.weight.device)
 
     def forward(self, ctx, h):
+        fed = ctx.fed_tokens is not None
+        if self.scale is not None or self.freq is not None:
+            ops.embed_scaled(h, self.weight, ctx.token_ids, ctx.positions, 1.0 if self.scale is None else float(self.scale), self.freq, ctx.status,
+                             ctx.token_src if fed else None, ctx.fed_tokens)
+            return
         ops.embed_gather(h, self.weight, ctx.token_ids, ctx.status, ctx.token_src if ctx.fed_tokens is not None else None, ctx.fed_tokens)
 
 class LinearHead(Part):

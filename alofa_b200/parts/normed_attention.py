@@ -1,0 +1,87 @@
+"""Softmax attention without rotation over a paged key/value cache, with the
+options of designs that take positions in by other means:
+
+* ``qk_norm``: q and k are divided by their root mean square over the head's
+  channels (eps inside the root, no weight);
+* ``q_temp_coef`` / ``q_temp_every``: the query at position p is multiplied by
+  ``1 + coef * ln(floor((p + 1) / every) + 1)``;
+* ``scale``: scores are ``(q . k) * scale``;
+* ``softcap``: then ``softcap * tanh(score / softcap)``;
+* keys of ``dim`` channels per head, values of ``vdim`` (the two caches have
+  their own widths); query head h reads key/value head ``h // (heads /
+  kv_heads)``; causal, all keys or the last ``window``.
+
+q, k and v come from one stacked projection whose fp32 sums a kernel norms,
+scales and writes to the query buffer and the tokens' cache slots.  Scores and
+softmax are fp32 in both compute dtypes."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..errors import AlofaError
+from .base import PagedKV, Part, TensorSpec, register_part
+from .linear import RESIDUAL, STORE, Linear, add_into_stream
+
+
+class NormedAttention(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.heads, self.kv_heads, self.dim, self.vdim = int(p("heads")), int(p("kv_heads")), int(p("dim")), int(p("vdim"))
+        self.scale = float(p("scale"))
+        self.softcap = float(self.params.get("softcap") or 0.0)
+        self.qk_norm = bool(self.params.get("qk_norm", False))
+        self.eps = float(self.params.get("eps") or 0.0)
+        self.coef = float(self.params.get("q_temp_coef") or 0.0)
+        self.every = int(self.params.get("q_temp_every") or 1)
+        self.window = self.params.get("window")
+        if min(self.heads, self.kv_heads, self.dim, self.vdim) <= 0 or self.heads % self.kv_heads:
+            raise AlofaError("invalid_argument", "kv heads must divide heads, sizes must be positive", f"params={self.params}")
+        if self.vdim > 256:
+            raise AlofaError("unsupported", "value heads of more than 256 channels", f"vdim={self.vdim}")
+        if self.every <= 0 or self.softcap < 0:
+            raise AlofaError("invalid_argument", "q_temp_every must be positive and softcap not negative", f"params={self.params}")
+        self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+
+    def cache_spec(self):
+        return PagedKV(self.kv_heads, self.dim, self.window, self.vdim)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * (self.q_dim + self.k_dim + self.v_dim) + 4 * self.q_dim + 4 * self.heads * self.vdim + 8 * self.hidden
+
+    def tensors(self):
+        pre = self.prefix
+        return {pre + "q": TensorSpec((self.q_dim, self.hidden)), pre + "k": TensorSpec((self.k_dim, self.hidden)), pre + "v": TensorSpec((self.v_dim, self.hidden)),
+                pre + "o": TensorSpec((self.hidden, self.heads * self.vdim))}
+
+    def load(self, state):
+        pre = self.prefix
+        self.qkv = Linear(torch.cat([state[pre + n] for n in "qkv"], dim=0), None, STORE)
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        if not writes:
+            raise AlofaError("unsupported", "this attention does not read another run's cache")
+        n, dt = x.shape[0], self.rt.dtype
+        group = ctx.groups[cache.group]
+        sums = ctx.buf((n, self.q_dim + self.k_dim + self.v_dim), torch.float32)
+        self.qkv(sums, x, buf=ctx.buf)
+        q = ctx.buf((n, self.q_dim), dt)
+        ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every)
+        out = ctx.buf((n, self.heads * self.vdim), dt)
+        ops.paged_attention_generic(out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size, self.heads, self.kv_heads,
+                                    self.dim, self.window, self.scale, self.softcap, self.vdim)
+        if store:
+            self.out_store(h, out, buf=ctx.buf)
+        else:
+            add_into_stream(ctx, self.out_add, h, out)
+
+
+register_part("mixer", "normed_attention", NormedAttention)

@@ -1,0 +1,177 @@
+"""Mixers that carry a state of fixed size per request instead of a growing
+cache: a state-space mixer with one scalar decay per head, and gated linear
+attention with one decay per key channel.  Both are the recurrence
+
+    S_t = diag(a_t) S_(t-1) + k_t v_t^T,    y_t = S_t^T q_t
+
+over a matrix state per head (key channels x value channels), run by one kernel
+(``ops.linear_scan``) that walks a request's tokens in order, in prompts and in
+decoding alike.  The state is fp32 and lives in the request's slot
+(:class:`~alofa_b200.parts.base.SlotState`); it is zero when a request starts.
+Decays, step sizes, softplus and exponentials, the norms and the gates are
+fp32 in both compute dtypes; bfloat16 only rounds the rows handed to the
+projections.
+
+``state_space``: ``[z | x | B | C | dt] = W_in h``; x, B and C pass a causal
+convolution per channel (``conv`` taps, bias, silu; the last ``conv - 1`` inputs
+are part of the state); ``dt = softplus(dt + dt_bias)``; per head, with the
+keys and queries of its group, ``a_t = exp(-exp(A_log) dt_t)``, ``k_t = dt_t
+B_t``, ``q_t = C_t``, ``y_t += D x_t``; then ``y * silu(z)``, an RMS norm in
+``norm_groups`` equal parts times a weight, and the output projection.
+
+``gated_linear_attention``: ``q = W_q h / sqrt(dim)``, ``k = W_k h``, ``v = W_v
+h``; ``a_t = sigmoid(W_a2 (W_a1 h) + b)^(1/tau)`` per key channel; each head's
+output is RMS-normed over its value channels with one weight shared by the
+heads, the heads are concatenated, multiplied by ``silu(W_g h)`` and projected."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..errors import AlofaError
+from .base import Part, SlotState, TensorSpec, as_float32_vector, register_part
+from .linear import RESIDUAL, STORE, Linear, add_into_stream
+
+# blocks a scan launch should have before its value channels stop being dealt to more of them
+SCAN_SPREAD = 296
+
+
+def _project_out(ctx, linear_add: Linear, linear_store: Linear, h, x, store: bool) -> None:
+    if store:
+        linear_store(h, x, buf=ctx.buf)
+    else:
+        add_into_stream(ctx, linear_add, h, x)
+
+
+class StateSpaceMixer(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.heads, self.vdim, self.state, self.groups = int(p("heads")), int(p("vdim")), int(p("state")), int(p("groups"))
+        self.taps, self.norm_groups, self.eps = int(p("conv")), int(p("norm_groups")), float(p("eps"))
+        if min(self.heads, self.vdim, self.state, self.groups, self.taps, self.norm_groups) <= 0 or self.heads % self.groups:
+            raise AlofaError("invalid_argument", "state-space sizes must be positive and groups must divide heads", f"params={self.params}")
+        self.inner = self.heads * self.vdim
+        if self.inner % self.norm_groups:
+            raise AlofaError("invalid_argument", "norm_groups must divide heads * vdim", f"inner={self.inner} norm_groups={self.norm_groups}")
+        self.bc = self.groups * self.state
+        self.channels = self.inner + 2 * self.bc  # what passes the convolution: x, B, C
+        self.in_rows = 2 * self.inner + 2 * self.bc + self.heads
+        self.conv_words = (self.taps - 1) * self.channels
+        self.scan_words = self.heads * self.vdim * self.state
+
+    def cache_spec(self):
+        # one fp32 vector per request: the recurrence's state [head][value][key], then the convolution's last inputs
+        return SlotState((self.scan_words + self.conv_words,), torch.float32)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * (self.in_rows + self.channels + 2 * self.inner) + 8 * self.hidden
+
+    def tensors(self):
+        pre = self.prefix
+        return {
+            pre + "in": TensorSpec((self.in_rows, self.hidden)),
+            pre + "conv": TensorSpec((self.channels, self.taps)),
+            pre + "conv.b": TensorSpec((self.channels,)),
+            pre + "dt_bias": TensorSpec((self.heads,)),
+            pre + "A_log": TensorSpec((self.heads,)),
+            pre + "D": TensorSpec((self.heads,), "ones"),
+            pre + "norm": TensorSpec((self.inner,), "ones"),
+            pre + "o": TensorSpec((self.hidden, self.inner)),
+        }
+
+    def load(self, state):
+        pre = self.prefix
+        self.w_in = Linear(state[pre + "in"], None, STORE)
+        self.conv_w = state[pre + "conv"].to(torch.float32).contiguous()
+        self.conv_b = as_float32_vector(state[pre + "conv.b"])
+        self.dt_bias = as_float32_vector(state[pre + "dt_bias"])
+        self.a_log = as_float32_vector(state[pre + "A_log"])
+        self.d_skip = as_float32_vector(state[pre + "D"])
+        self.norm_w = as_float32_vector(state[pre + "norm"])
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        n, f32 = x.shape[0], torch.float32
+        inner, bc = self.inner, self.bc
+        u = ctx.buf((n, self.in_rows), f32)  # [z | x | B | C | dt], the projection's fp32 sums
+        self.w_in(u, x, buf=ctx.buf)
+        st = cache.state
+        xbc = ctx.buf((n, self.channels), f32)
+        ops.causal_conv(xbc, u, inner, self.conv_w, self.conv_b, st[:, self.scan_words:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs)
+        y = ctx.buf((n, inner), f32)
+        ops.linear_scan(y, xbc, 0, xbc, inner, xbc, inner + bc, u, 2 * inner + 2 * bc, st, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.groups,
+                        self.state, self.vdim, 0, dt_bias=self.dt_bias, a_log=self.a_log, d_skip=self.d_skip, spread=SCAN_SPREAD)
+        normed = ctx.buf((n, inner), self.rt.dtype)
+        ops.gated_group_norm(normed, y, u, 0, self.norm_w, self.norm_groups, self.eps, gate_first=True)
+        _project_out(ctx, self.out_add, self.out_store, h, normed, store)
+
+
+class GatedLinearAttention(Part):
+    family = "mixer"
+    graph_safe = True
+    stores_output = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.param
+        self.hidden = int(p("hidden_size"))
+        self.heads, self.dim, self.vdim = int(p("heads")), int(p("dim")), int(p("vdim"))
+        self.tau, self.eps = float(p("tau")), float(p("eps"))
+        if min(self.heads, self.dim, self.vdim) <= 0 or self.tau <= 0:
+            raise AlofaError("invalid_argument", "gated linear attention sizes and tau must be positive", f"params={self.params}")
+        self.qk, self.v = self.heads * self.dim, self.heads * self.vdim
+        self.rows = 2 * self.qk + 2 * self.v  # [q | k | v | g]
+        self.rank = None  # the decay's inner size, from the tensor's shape
+
+    def cache_spec(self):
+        return SlotState((self.heads * self.vdim * self.dim,), torch.float32)
+
+    def scratch_row_bytes(self) -> int:
+        return 4 * (self.rows + self.qk + 2 * self.v) + 8 * self.hidden + 64
+
+    def tensors(self):
+        pre = self.prefix
+        rank = -int(self.params.get("decay_rank") or 16)  # the decay's inner size is the tensors' own; this many for random weights
+        return {
+            pre + "q": TensorSpec((self.qk, self.hidden)), pre + "k": TensorSpec((self.qk, self.hidden)), pre + "v": TensorSpec((self.v, self.hidden)),
+            pre + "g": TensorSpec((self.v, self.hidden)), pre + "o": TensorSpec((self.hidden, self.v)), pre + "norm": TensorSpec((self.vdim,), "ones"),
+            pre + "a1": TensorSpec((rank, self.hidden)), pre + "a2": TensorSpec((self.qk, rank)), pre + "a2.b": TensorSpec((self.qk,)),
+        }
+
+    def load(self, state):
+        pre = self.prefix
+        self.w_in = Linear(torch.cat([state[pre + n] for n in ("q", "k", "v", "g")], dim=0), None, STORE)
+        self.a1 = Linear(state[pre + "a1"], None, STORE)
+        self.a2 = Linear(state[pre + "a2"], as_float32_vector(state[pre + "a2.b"]), STORE)
+        self.rank = state[pre + "a1"].shape[0]
+        if state[pre + "a2"].shape[1] != self.rank:
+            raise AlofaError("invalid_argument", "the two decay projections disagree about their inner size", f"a1={tuple(state[pre + 'a1'].shape)} a2={tuple(state[pre + 'a2'].shape)}")
+        self.norm_w = as_float32_vector(state[pre + "norm"])
+        self.out_add = Linear(state[pre + "o"], None, RESIDUAL)
+        self.out_store = Linear(state[pre + "o"], None, STORE)
+
+    def forward(self, ctx, x, h, cache, writes=True, store=False):
+        n, f32 = x.shape[0], torch.float32
+        u = ctx.buf((n, self.rows), f32)  # [q | k | v | g]
+        self.w_in(u, x, buf=ctx.buf)
+        low = ctx.buf((n, self.rank), self.rt.dtype)
+        self.a1(low, x, buf=ctx.buf)
+        z = ctx.buf((n, self.qk), f32)  # the decays' logits, one per key channel
+        self.a2(z, low, buf=ctx.buf)
+        y = ctx.buf((n, self.v), f32)
+        ops.linear_scan(y, u, 2 * self.qk, u, self.qk, u, 0, z, 0, cache.state, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.heads, self.dim,
+                        self.vdim, 1, tau=self.tau, q_scale=self.dim ** -0.5, spread=SCAN_SPREAD)
+        normed = ctx.buf((n, self.v), self.rt.dtype)
+        ops.gated_group_norm(normed, y, u, 2 * self.qk + self.v, self.norm_w, self.heads, self.eps, gate_first=False)
+        _project_out(ctx, self.out_add, self.out_store, h, normed, store)
+
+
+register_part("mixer", "state_space", StateSpaceMixer)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)

@@ -5,7 +5,12 @@ every token uses ``top``.  Router logits ``z = x Wr^T`` and the scores made from
 them are fp32 (``score``: "sigmoid" per expert, or "softmax" over the experts);
 the ``top`` largest scores choose the experts and are their weights
 (``renormalize``: divided by their sum).  The weight multiplies the expert's
-input (``weight_on_input``) or its output.  A shared expert of the same form
+input (``weight_on_input``) or its output.  Options: ``gated`` experts
+``Wdown (act(Wgate .) * (Wup .))`` (tensors ``e<i>.gate``); ``correction``, a
+stored vector added to the scores for the choice only (the weights stay the
+scores); ``identity``: the last so many of the router's outputs are experts
+without tensors whose output is their input; ``renorm_eps`` added to the sum
+that ``renormalize`` divides by.  A shared expert of the same form
 (``shared_ff`` > 0) runs for every token and is added, times ``sigmoid(x
 wsg^T)`` when ``shared_gate`` is set.
 
@@ -44,9 +49,18 @@ class RoutedExperts(Part):
         self.renormalize = bool(self.params.get("renormalize", False))
         self.weight_on_input = bool(self.params.get("weight_on_input", False))
         self.shared_gate = bool(self.params.get("shared_gate", False)) and self.shared_ff > 0
+        self.gated = bool(self.params.get("gated", False))
+        self.identity = int(self.params.get("identity") or 0)
+        self.correction_name = self.prefix + "correction" if self.params.get("correction") else None
+        self.renorm_eps = float(self.params.get("renorm_eps") or 0.0)
+        self.routed = self.experts + self.identity  # outputs of the router
+        if self.gated and self.act != "silu":
+            raise AlofaError("unsupported", "gated experts take the silu activation only", f"activation={self.act}")
+        if self.identity and self.weight_on_input:
+            raise AlofaError("unsupported", "identity experts need the weight on the expert's output")
         if self.act not in ops.ACTIVATIONS or self.score not in ("sigmoid", "softmax"):
             raise AlofaError("unsupported", "unknown activation or score of a routed feed-forward", f"activation={self.act} score={self.score}")
-        if not 0 < self.top <= min(self.experts, 32):
+        if not 0 < self.top <= min(self.experts + int(self.params.get("identity") or 0), 32) or self.experts <= 0:
             raise AlofaError("invalid_argument", "top must lie in [1, min(experts, 32)]", f"top={self.top} experts={self.experts}")
         self.shared = None
         if self.shared_ff:
@@ -57,8 +71,12 @@ class RoutedExperts(Part):
 
     def tensors(self):
         pre = self.prefix
-        t = {pre + "router": TensorSpec((self.experts, self.hidden))}
+        t = {pre + "router": TensorSpec((self.routed, self.hidden))}
+        if self.correction_name:
+            t[self.correction_name] = TensorSpec((self.routed,))
         for e in range(self.experts):
+            if self.gated:
+                t[pre + f"e{e}.gate"] = TensorSpec((self.ff, self.hidden))
             t[pre + f"e{e}.up"] = TensorSpec((self.ff, self.hidden))
             t[pre + f"e{e}.down"] = TensorSpec((self.hidden, self.ff))
         if self.shared is not None:
@@ -71,13 +89,17 @@ class RoutedExperts(Part):
         pre = self.prefix
         rows = [state[pre + "router"]] + ([state[pre + "shared.sg"]] if self.shared_gate else [])
         self.router = torch.cat(rows, dim=0).to(torch.float32).contiguous()  # the router is fp32 whatever the compute dtype
-        self.up = torch.stack([state[pre + f"e{e}.up"] for e in range(self.experts)]).contiguous()  # [E, ff, hidden]
+        if self.gated:  # gate rows first, then up rows: one product yields both
+            self.up = torch.stack([torch.cat([state[pre + f"e{e}.gate"], state[pre + f"e{e}.up"]], dim=0) for e in range(self.experts)]).contiguous()
+        else:
+            self.up = torch.stack([state[pre + f"e{e}.up"] for e in range(self.experts)]).contiguous()  # [E, ff, hidden]
+        self.correction = state[self.correction_name].to(torch.float32).contiguous() if self.correction_name else None
         self.down = torch.stack([state[pre + f"e{e}.down"] for e in range(self.experts)]).contiguous()  # [E, hidden, ff]
         if self.shared is not None:
             self.shared.load(state)
 
     def scratch_row_bytes(self) -> int:
-        return 2 * self.top * (4 * self.hidden + 4 * self.ff + 4 * self.hidden) + 8 * self.hidden + 4 * self.shared_ff + 4 * (self.experts + 1)
+        return 2 * self.top * (4 * self.hidden + (12 if self.gated else 4) * self.ff + 4 * self.hidden) + 8 * self.hidden + 4 * self.shared_ff + 4 * (self.experts + 1)
 
     def forward(self, ctx, x, h, store=False):
         n, dt, top = x.shape[0], self.rt.dtype, self.top
@@ -86,7 +108,7 @@ class RoutedExperts(Part):
         i32, f32 = torch.int32, torch.float32
         choice, weight = ctx.buf((n, top), i32), ctx.buf((n, top), f32)
         gate = ctx.buf((n,), f32) if self.shared_gate else None
-        ops.moe_router(choice, weight, gate, x, self.router, self.experts, top, self.score == "softmax", self.renormalize)
+        ops.moe_router(choice, weight, gate, x, self.router, self.routed, top, self.score == "softmax", self.renormalize, self.correction, self.renorm_eps)
         pairs = n * top
         tiles = -(-pairs // tile) + self.experts  # every expert may end on a tile that is not full
         dest, tile_expert = ctx.buf((n, top), i32), ctx.buf((tiles,), i32)
@@ -95,17 +117,20 @@ class RoutedExperts(Part):
         xs = ctx.buf((rows, self.hidden), dt)
         ops.moe_scatter(xs, x, weight if self.weight_on_input else None, dest, top)
         mid = ctx.buf((rows, self.ff), dt)
-        ops.gemm_by_tile(mid, xs, self.up, tile_expert, tile, act=self.act)
+        if self.gated:
+            both = ctx.buf((rows, 2 * self.ff), f32)
+            ops.gemm_by_tile(both, xs, self.up, tile_expert, tile)
+            ops.gate_up(mid, both)
+        else:
+            ops.gemm_by_tile(mid, xs, self.up, tile_expert, tile, act=self.act)
         ys = ctx.buf((rows, self.hidden), f32)
         ops.gemm_by_tile(ys, mid, self.down, tile_expert, tile)
         shared = None
         if self.shared is not None:
             shared = ctx.buf((n, self.hidden), f32)
             self.shared.forward(ctx, x, shared, store=True)
-        y = h if store else ctx.buf((n, self.hidden), f32)
-        ops.moe_combine(y, ys, dest, None if self.weight_on_input else weight, shared, gate, top)
-        if not store:
-            h.add_(y)
+        # written when the caller wants the output alone, else added into the stream in the same kernel
+        ops.moe_combine(h, ys, dest, None if self.weight_on_input else weight, shared, gate, top, x if self.identity else None, add=not store)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

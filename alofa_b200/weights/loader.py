@@ -33,6 +33,13 @@ from ..errors import AlofaError
 from .safetensors_io import SafeTensorFile
 
 
+def shape_fits(found, want) -> bool:
+    """A negative entry of ``want`` stands for a size the file decides (its
+    magnitude is what random weights use)."""
+    found, want = tuple(found), tuple(want)
+    return len(found) == len(want) and all(w < 0 or f == w for f, w in zip(found, want))
+
+
 def check_names_and_shapes(expected: dict, found: dict, origin: str) -> None:
     """``expected``: name -> TensorSpec; ``found``: name -> shape tuple."""
     missing = [n for n, s in expected.items() if n not in found and not s.optional]
@@ -40,7 +47,7 @@ def check_names_and_shapes(expected: dict, found: dict, origin: str) -> None:
     wrong = [
         f"{n} got={tuple(found[n])} want={tuple(s.shape)}"
         for n, s in expected.items()
-        if n in found and tuple(found[n]) != tuple(s.shape)
+        if n in found and not shape_fits(found[n], s.shape)
     ]
     if missing or unexpected or wrong:
         parts = []

@@ -26,7 +26,7 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(seed: int, name: str, shape, init: str, dtype, device="cpu") -> torch.Tensor:
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
-    x = torch.randn(tuple(shape), generator=gen, dtype=torch.float32, device=device)
+    x = torch.randn(tuple(abs(d) for d in shape), generator=gen, dtype=torch.float32, device=device)
     if init == "normal":
         x.mul_(0.02)
     elif init == "ones":
