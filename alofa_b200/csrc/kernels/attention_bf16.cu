@@ -41,6 +41,9 @@ struct AttnParams {
   float* partial_ml;     // split mode: [splits, T * nh, 2]
   int max_blocks, page_size, nh, nkv, window, split_keys, n_splits, n_rows_total, table_entries;
   float scale_log2;      // scale * log2(e)
+#ifdef SOFTCAP
+  float cap_in, cap_out;  // scale / softcap and softcap / scale: scores are cap_out * tanh(dot * cap_in) before the scale
+#endif
   int* status;           // set to 2 when a wait on a bulk copy gave up (may be null)
 };
 
@@ -212,6 +215,12 @@ __global__ void __launch_bounds__(128) attention_bf16_kernel(const AttnParams p)
         mma_16816(s[2 * n2 + 1], qf[ks], kf[2], kf[3]);
       }
     }
+#ifdef SOFTCAP
+#pragma unroll
+    for (int n = 0; n < BLOCK_N / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[n][e] = cap_score(s[n][e], p.cap_in, p.cap_out);
+#endif
     // ---- visibility -------------------------------------------------------------
     const int j0 = nb * BLOCK_N;
     const bool all_visible = (j0 + BLOCK_N - 1 <= min(warp_pos_min, k_hi)) && (j0 >= k_lo) &&
@@ -480,7 +489,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         if (LONG && lane == 0 && block + 2 * WARPS <= last) row_after = block_row(block + 2 * WARPS);
         bool values_here = true;
         attend_block<true>(
-            st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2,
+            st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2 CAP_ARGS(p),
             [&] {
               if (more) {
                 __syncwarp();  // every lane has taken its scores from the key tile
@@ -497,7 +506,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_decode_kernel(const Attn
         }
         row_next = row_after;
       } else {
-        attend_block<false>(st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2);
+        attend_block<false>(st, qf, kt_s, vt_s, block * BLOCK_N, lane, pos, k_lo, k_hi, p.window, p.scale_log2 CAP_ARGS(p));
         if (more) {
           __syncwarp();
           fetch_padded(block + WARPS);
@@ -678,8 +687,13 @@ ALOFA_API int alofa_attention_combine(void* out, const float* partial_o, const f
 ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache, const int* q_start, const int* kv_len, const int* positions,
                                    const int* block_table, int max_blocks, int page_size, int n_seqs, int n_tokens, int tiles, int nh, int nkv,
                                    int window, float scale, int n_splits, int split_keys, float* partial_o, float* partial_ml,
-                                   int max_kv_len, long long cache_slots, int* status, int do_combine, cudaStream_t stream) {
+                                   int max_kv_len, long long cache_slots, int* status, int do_combine, float softcap, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
+#ifdef SOFTCAP
+  if (!(softcap > 0.f) || !(scale > 0.f)) return ALOFA_ERR_ARGUMENT;
+#else
+  if (softcap != 0.f) return ALOFA_ERR_ARGUMENT;  // only a library built with SOFTCAP caps its scores
+#endif
   if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || tiles <= 0) return ALOFA_ERR_ARGUMENT;
   if (n_splits > 0 && (split_keys <= 0 || split_keys % BLOCK_N != 0 || !partial_o || !partial_ml || !positions)) return ALOFA_ERR_ARGUMENT;
   const bool decode_only = n_seqs == n_tokens;
@@ -704,6 +718,10 @@ ALOFA_API int alofa_attention_bf16(void* out, const void* q, const void* k_cache
   p.n_splits = n_splits > 0 ? n_splits : 1;
   p.n_rows_total = n_tokens * nh;
   p.scale_log2 = scale * 1.4426950408889634f;
+#ifdef SOFTCAP
+  p.cap_in = scale / softcap;
+  p.cap_out = softcap / scale;
+#endif
   // entries of a block table one CTA may touch: a split's keys, or up to the longest request
   const int reach = n_splits > 0 ? split_keys : max_kv_len;
   p.table_entries = reach / page_size + 2;

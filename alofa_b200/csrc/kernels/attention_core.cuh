@@ -69,12 +69,32 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t base, int row, int col) {
   return base + (row * ROW + col) * 2;
 }
 
+// A library built with SOFTCAP bounds the scaled scores by softcap * tanh(score / softcap) before the
+// softmax: the raw dot products are turned into cap_out * tanh(dot * cap_in) with cap_in = scale / softcap
+// and cap_out = softcap / scale, after which the scale is folded into the exponent as ever.  The
+// hyperbolic tangent is the hardware's approximation (relative error 2^-11, less than what the bfloat16
+// rounding of queries and keys leaves in a score); the 32-bit path uses the library function.
+#ifdef SOFTCAP
+#define CAP_PARAMS , float cap_in, float cap_out
+#define CAP_PASS , cap_in, cap_out
+#define CAP_ARGS(p) , (p).cap_in, (p).cap_out
+__device__ __forceinline__ float cap_score(float dot, float cap_in, float cap_out) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(dot * cap_in));
+  return cap_out * t;
+}
+#else
+#define CAP_PARAMS
+#define CAP_PASS
+#define CAP_ARGS(p)
+#endif
+
 // One warp: 16 query rows against the 64 keys of one block held in shared tiles.
 // keys_done() runs when the key tile has been read for the last time (it may be
 // refilled), values_wanted() just before the value tile is read for the first time.
 template <bool SWIZZLED, class KeysDone, class ValuesWanted>
 __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], uint32_t kt, uint32_t vt, int j0, int lane,
-                                             int pos, int k_lo, int k_hi, int window, float scale_log2, KeysDone keys_done,
+                                             int pos, int k_lo, int k_hi, int window, float scale_log2 CAP_PARAMS, KeysDone keys_done,
                                              ValuesWanted values_wanted) {
   float s[BLOCK_N / 8][4];
 #pragma unroll
@@ -90,6 +110,12 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
     }
   }
   keys_done();
+#ifdef SOFTCAP
+#pragma unroll
+  for (int n = 0; n < BLOCK_N / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[n][e] = cap_score(s[n][e], cap_in, cap_out);
+#endif
   const bool all_visible = j0 >= k_lo && j0 + BLOCK_N - 1 <= k_hi && (window <= 0 || j0 > pos - window);
   if (!all_visible) {
 #pragma unroll
@@ -154,8 +180,8 @@ __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[
 
 template <bool SWIZZLED>
 __device__ __forceinline__ void attend_block(RowState& st, const uint32_t (&qf)[KSTEPS][4], uint32_t kt, uint32_t vt, int j0, int lane,
-                                             int pos, int k_lo, int k_hi, int window, float scale_log2) {
-  attend_block<SWIZZLED>(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, window, scale_log2, [] {}, [] {});
+                                             int pos, int k_lo, int k_hi, int window, float scale_log2 CAP_PARAMS) {
+  attend_block<SWIZZLED>(st, qf, kt, vt, j0, lane, pos, k_lo, k_hi, window, scale_log2 CAP_PASS, [] {}, [] {});
 }
 
 constexpr int MERGE_ROW = HD + 4;  // floats per merged row in shared memory

@@ -232,6 +232,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attention_prefill_tc_kernel(con
         for (int j = 0; j < 16; ++j) s[c0 + j] = __uint_as_float(v[j]);
       }
       tmem_ld_wait();
+#ifdef SOFTCAP
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) s[j] = cap_score(s[j], p.cap_in, p.cap_out);
+#endif
       const int j0 = (jb0 + i) * TC_BN + half * COLS;
       const bool all_visible = row_ok && j0 + COLS - 1 <= my_pos && j0 >= my_lo;
       if (!all_visible) {

@@ -87,13 +87,17 @@ def _gemm_tc():
     return lib
 
 
-def _attention(head_dim: int):
-    key = f"attention_hd{head_dim}"
+def _attention(head_dim: int, capped: bool = False):
+    """The attention library of one head size; ``capped``: the build whose scores are bounded by softcap * tanh(. / softcap)."""
+    key = f"attention_hd{head_dim}" + ("_cap" if capped else "")
     lib = _libs.get(key)
     if lib is None:
-        lib = load_library(f"alofa_attention_hd{head_dim}", ["kernels/attention_bf16.cu"], defines={"HEAD_DIM": head_dim})
+        defines = {"HEAD_DIM": head_dim}
+        if capped:
+            defines["SOFTCAP"] = 1
+        lib = load_library(f"alofa_{key}", ["kernels/attention_bf16.cu"], defines=defines)
         lib.alofa_attention_bf16.restype = _I
-        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _P]
+        lib.alofa_attention_bf16.argtypes = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, ctypes.c_longlong, _P, _I, _F, _P]
         lib.alofa_attention_combine.restype = _I
         lib.alofa_attention_combine.argtypes = [_P, _P, _P, _P, _I, _I, _I, _I, _P]
         lib.alofa_attention_decode_wide_warps.restype = _I
@@ -107,19 +111,19 @@ def _attention(head_dim: int):
 _decode_slots = {}
 
 
-def attention_decode_wide_warps(head_dim: int) -> int:
+def attention_decode_wide_warps(head_dim: int, capped: bool = False) -> int:
     """Warps of the decode attention kernel's wide form at this head size (one
     CTA per SM; its splits are multiples of 64 keys a warp), 0 when it has none."""
-    return _attention(head_dim).alofa_attention_decode_wide_warps()
+    return _attention(head_dim, capped).alofa_attention_decode_wide_warps()
 
 
-def attention_decode_slots(head_dim: int, page_size: int, warps: int = 4) -> int:
+def attention_decode_slots(head_dim: int, page_size: int, warps: int = 4, capped: bool = False) -> int:
     """How many CTAs of the decode attention kernel with ``warps`` warps (4, or
     the wide form's) the device holds at a time, 0 when that kernel is not
     built for this head size and kind of page (asked once each)."""
-    key = (head_dim, page_size % 64 == 0, warps)
+    key = (head_dim, page_size % 64 == 0, warps, capped)
     if key not in _decode_slots:
-        _decode_slots[key] = max(0, _attention(head_dim).alofa_attention_decode_slots(page_size, warps))
+        _decode_slots[key] = max(0, _attention(head_dim, capped).alofa_attention_decode_slots(page_size, warps))
     return _decode_slots[key]
 
 
@@ -447,17 +451,19 @@ def gemm_tc_rope(x, w, bias, q_out, k_cache, v_cache, slot_map, positions, cos_s
 
 
 def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_table, page_size, n_seqs, max_q_len, nh, nkv, hd, window, scale,
-                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None, combine: bool = True) -> None:
+                   n_splits: int = 0, split_keys: int = 0, partial_o=None, partial_ml=None, max_kv_len: int = 0, status=None, combine: bool = True, softcap: float = 0.0) -> None:
     """Causal GQA over the paged bf16 cache for a step's requests; with
     ``n_splits`` > 0 the keys of each request (decode tokens) or of each query
     tile (prompt portions) are split over several CTAs and merged - unless
     ``combine`` is False (decode tokens only): then ``partial_o`` / ``partial_ml``
-    keep the splits for :func:`attention_combine` or a product that merges them."""
+    keep the splits for :func:`attention_combine` or a product that merges them.
+    ``softcap`` > 0 (the library built for it): scaled scores are bounded by
+    ``softcap * tanh(score / softcap)``."""
     n = q.shape[0]
     bf = torch.bfloat16
     g = nh // nkv
     tiles = -(-(max_q_len * g) // 64)
-    rc = _attention(hd).alofa_attention_bf16(
+    rc = _attention(hd, softcap > 0).alofa_attention_bf16(
         _dev(out, "out", bf), _dev(q, "q", bf), _dev(k_cache, "k_cache", bf), _dev(v_cache, "v_cache", bf),
         _dev(q_start, "q_start", torch.int32), _dev(kv_len, "kv_len", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32),
@@ -465,7 +471,7 @@ def attention_bf16(out, q, k_cache, v_cache, q_start, kv_len, positions, block_t
         _dev(partial_o, "partial_o", torch.float32) if partial_o is not None else None,
         _dev(partial_ml, "partial_ml", torch.float32) if partial_ml is not None else None,
         int(max_kv_len) if max_kv_len else block_table.shape[1] * page_size, k_cache.shape[0],
-        _dev(status, "status", torch.int32) if status is not None else None, 1 if combine else 0, _stream(),
+        _dev(status, "status", torch.int32) if status is not None else None, 1 if combine else 0, float(softcap or 0.0), _stream(),
     )
     _done(rc, "attention_bf16", f"hd={hd} nh={nh} nkv={nkv} splits={n_splits}")
     if n_splits > 1 and combine:

@@ -24,7 +24,107 @@ from .base import PagedKV, Part, TensorSpec, as_float32_vector, build_part, regi
 from .linear import RESIDUAL, STORE, Linear, MergedSplits, add_into_stream
 
 
-class GQAttention(Part):
+class PagedAttend:
+    """Attention of a step's rows over a paged key/value cache, shared by the
+    mixers that keep one: which kernel runs, and how a decode step's keys are
+    split over CTAs.  The mixer gives ``nh``, ``nkv``, ``hd`` (keys and values
+    alike), ``q_dim``, ``window``, ``scale`` and ``softcap`` (0: none)."""
+
+    softcap = 0.0
+
+    # Keys per CTA, at least, when a decode-only step splits each request's keys: four 64-key
+    # blocks, one per warp.  Splits grow in steps of this (a warp then takes several blocks in
+    # turn, fetching the next behind its work on this one) until the step's CTAs are resident
+    # together: CTAs that queue for an SM load, then compute, wave after wave (batch 64 at
+    # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
+    # of 128 on 4).
+    SPLIT_KEYS = 256
+    # On pages of whole key blocks head sizes 64 and 128 have a wide form of the kernel, one CTA per SM with
+    # eight or six warps (what shared memory holds tiles for), whose splits grow by 64 keys a warp: fewer,
+    # larger CTAs and fewer splits to merge (14 heads of 64 on 2, batch 8: nine splits of 256 keys 0.780 ms per
+    # step, five of 512 0.758; batch 12: 0.819 -> 0.788; 28 heads of 128 on 4, batch 64: 5.03 -> 4.90 ms).  With
+    # three tenths as many (request, KV head) pairs as SMs or more, in steps of more than 16 tokens, one split
+    # per pair (14 heads of 64 on 2, batch 64: 1.40 -> 1.34 ms; batch 32: 1.065 -> 1.027; the merge kernel and
+    # the partial sums go).
+    # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
+    # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
+    # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
+    PROMPT_SPLIT_KEYS = 0
+
+    # Decode tokens in at most this many key splits are handed to the output product unmerged: it
+    # merges them while it loads its operand, which saves a kernel; with more splits every CTA of
+    # the product would re-read too many partial outputs.
+    MERGE_IN_PRODUCT_SPLITS = 16
+
+    @classmethod
+    def decode_split_keys(cls, n_tokens: int, pairs: int, longest: int, longest_now: int, wide_slots: int, slots: int, wide_unit: int = 512) -> int:
+        """Keys per CTA of a decode-only step.  ``pairs``: (request, KV head)
+        pairs; ``longest``: the context the launch must cover (a graph's
+        bucket), ``longest_now``: the longest context of this step;
+        ``wide_slots`` / ``slots``: CTAs of the wide / four-warp kernel the
+        device holds at a time (0: that kernel is not built here);
+        ``wide_unit``: the keys the wide kernel's splits grow by."""
+        pairs = max(1, pairs)
+        # the unit a split grows by, and how many CTAs of that kernel are resident together
+        unit, room = (wide_unit, wide_slots) if wide_slots > 0 else (cls.SPLIT_KEYS, slots)
+        whole = unit * -(-longest // unit)
+        if wide_slots > 0 and n_tokens > 16 and 10 * pairs >= 3 * wide_slots:
+            # enough pairs to keep the SMs busy with one CTA each: the whole context in one split, no partial
+            # sums and no kernel that merges them
+            return whole
+        # as many splits as are resident together, by the longest context of this step (a graph keeps what the
+        # step that recorded it chose; every length its bucket holds is covered either way)
+        blocks = -(-max(1, longest_now) // unit)
+        per_split = unit * -(-blocks // max(1, room // pairs))
+        if per_split >= blocks * unit:
+            return whole  # one split: let it reach to the end of the bucket, so that nothing is merged
+        if n_tokens <= 16 and longest <= 4 * cls.MERGE_IN_PRODUCT_SPLITS * cls.SPLIT_KEYS:
+            # few enough splits that the output product merges them, while a warp has at most a few blocks
+            per_split = max(per_split, unit * -(-longest // (unit * cls.MERGE_IN_PRODUCT_SPLITS)))
+        return per_split
+
+    def attend(self, ctx, q, cache, group):
+        """Attention of the step's rows over the cache: the tensor-core kernels
+        for bfloat16 and head sizes they are built for, else the generic one.
+        Returns the output rows, or a :class:`MergedSplits` for the product
+        that follows to merge."""
+        out = ctx.buf((q.shape[0], self.q_dim), q.dtype)
+        if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
+            splits, po, pml = 0, None, None
+            longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
+            per_split = self.SPLIT_KEYS
+            group_size = self.nh // self.nkv
+            if ctx.decode_only and group_size <= 16:
+                capped = self.softcap > 0
+                wide_warps = ops.attention_decode_wide_warps(self.hd, capped)
+                per_split = self.decode_split_keys(ctx.n_tokens, ctx.n_seqs * self.nkv, longest, ctx.max_kv_len,
+                                                   ops.attention_decode_slots(self.hd, group.page_size, wide_warps, capped) if wide_warps else 0,
+                                                   ops.attention_decode_slots(self.hd, group.page_size, 4, capped), 64 * wide_warps)
+            if not ctx.decode_only:
+                per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
+            if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):
+                splits = max(1, -(-longest // per_split))
+            elif not ctx.decode_only and longest > per_split:
+                splits = -(-longest // per_split)
+            if splits:
+                po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
+                pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
+            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16
+            ops.attention_bf16(
+                out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
+                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged, softcap=self.softcap,
+            )
+            if unmerged:
+                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf)
+            return out
+        ops.paged_attention_generic(
+            out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
+            self.nh, self.nkv, self.hd, self.window, self.scale, self.softcap,
+        )
+        return out
+
+
+class GQAttention(PagedAttend, Part):
     family = "mixer"
 
     @property
@@ -148,96 +248,6 @@ class GQAttention(Part):
                 k_view = qkv[:, self.q_dim : self.q_dim + nkv_in * self.hd].view(n, nkv_in, self.hd)
                 custom(ctx, q_view, k_view)
             ops.rope_store(q, cache.k, cache.v, qkv, table, ctx.positions, group.slot_map, self.nh, nkv_in, self.hd, rot, writes)
-
-    # Keys per CTA, at least, when a decode-only step splits each request's keys: four 64-key
-    # blocks, one per warp.  Splits grow in steps of this (a warp then takes several blocks in
-    # turn, fetching the next behind its work on this one) until the step's CTAs are resident
-    # together: CTAs that queue for an SM load, then compute, wave after wave (batch 64 at
-    # 2,048 keys: 1.58 -> 1.47 ms per step for 14 heads of 64 on 2, 5.90 -> 5.08 ms for 28 heads
-    # of 128 on 4).
-    SPLIT_KEYS = 256
-    # On pages of whole key blocks head sizes 64 and 128 have a wide form of the kernel, one CTA per SM with
-    # eight or six warps (what shared memory holds tiles for), whose splits grow by 64 keys a warp: fewer,
-    # larger CTAs and fewer splits to merge (14 heads of 64 on 2, batch 8: nine splits of 256 keys 0.780 ms per
-    # step, five of 512 0.758; batch 12: 0.819 -> 0.788; 28 heads of 128 on 4, batch 64: 5.03 -> 4.90 ms).  With
-    # three tenths as many (request, KV head) pairs as SMs or more, in steps of more than 16 tokens, one split
-    # per pair (14 heads of 64 on 2, batch 64: 1.40 -> 1.34 ms; batch 32: 1.065 -> 1.027; the merge kernel and
-    # the partial sums go).
-    # Keys per CTA when a step with prompt portions splits the keys of its query tiles; 0 = never.
-    # Measured at 2,048-token prompts the round trip of the partial sums costs more than the
-    # long tiles' tail saves (4.9 ms against 4.5 ms for the step), so it is off.
-    PROMPT_SPLIT_KEYS = 0
-
-    # Decode tokens in at most this many key splits are handed to the output product unmerged: it
-    # merges them while it loads its operand, which saves a kernel; with more splits every CTA of
-    # the product would re-read too many partial outputs.
-    MERGE_IN_PRODUCT_SPLITS = 16
-
-    @classmethod
-    def decode_split_keys(cls, n_tokens: int, pairs: int, longest: int, longest_now: int, wide_slots: int, slots: int, wide_unit: int = 512) -> int:
-        """Keys per CTA of a decode-only step.  ``pairs``: (request, KV head)
-        pairs; ``longest``: the context the launch must cover (a graph's
-        bucket), ``longest_now``: the longest context of this step;
-        ``wide_slots`` / ``slots``: CTAs of the wide / four-warp kernel the
-        device holds at a time (0: that kernel is not built here);
-        ``wide_unit``: the keys the wide kernel's splits grow by."""
-        pairs = max(1, pairs)
-        # the unit a split grows by, and how many CTAs of that kernel are resident together
-        unit, room = (wide_unit, wide_slots) if wide_slots > 0 else (cls.SPLIT_KEYS, slots)
-        whole = unit * -(-longest // unit)
-        if wide_slots > 0 and n_tokens > 16 and 10 * pairs >= 3 * wide_slots:
-            # enough pairs to keep the SMs busy with one CTA each: the whole context in one split, no partial
-            # sums and no kernel that merges them
-            return whole
-        # as many splits as are resident together, by the longest context of this step (a graph keeps what the
-        # step that recorded it chose; every length its bucket holds is covered either way)
-        blocks = -(-max(1, longest_now) // unit)
-        per_split = unit * -(-blocks // max(1, room // pairs))
-        if per_split >= blocks * unit:
-            return whole  # one split: let it reach to the end of the bucket, so that nothing is merged
-        if n_tokens <= 16 and longest <= 4 * cls.MERGE_IN_PRODUCT_SPLITS * cls.SPLIT_KEYS:
-            # few enough splits that the output product merges them, while a warp has at most a few blocks
-            per_split = max(per_split, unit * -(-longest // (unit * cls.MERGE_IN_PRODUCT_SPLITS)))
-        return per_split
-
-    def attend(self, ctx, q, cache, group):
-        """Attention of the step's rows over the cache: the tensor-core kernels
-        for bfloat16 and head sizes they are built for, else the generic one.
-        Returns the output rows, or a :class:`MergedSplits` for the product
-        that follows to merge."""
-        out = ctx.buf((q.shape[0], self.q_dim), q.dtype)
-        if q.dtype == torch.bfloat16 and ops.attention_bf16_supported(self.hd):
-            splits, po, pml = 0, None, None
-            longest = ctx.max_context if ctx.capturing else ctx.max_kv_len
-            per_split = self.SPLIT_KEYS
-            group_size = self.nh // self.nkv
-            if ctx.decode_only and group_size <= 16:
-                wide_warps = ops.attention_decode_wide_warps(self.hd)
-                per_split = self.decode_split_keys(ctx.n_tokens, ctx.n_seqs * self.nkv, longest, ctx.max_kv_len,
-                                                   ops.attention_decode_slots(self.hd, group.page_size, wide_warps) if wide_warps else 0,
-                                                   ops.attention_decode_slots(self.hd, group.page_size), 64 * wide_warps)
-            if not ctx.decode_only:
-                per_split = self.PROMPT_SPLIT_KEYS or (1 << 30)
-            if ctx.decode_only and self.nh // self.nkv <= 64 and (longest > per_split or self.nh // self.nkv <= 16):
-                splits = max(1, -(-longest // per_split))
-            elif not ctx.decode_only and longest > per_split:
-                splits = -(-longest // per_split)
-            if splits:
-                po = ctx.buf((splits, ctx.n_tokens * self.nh, self.hd), torch.float32)
-                pml = ctx.buf((splits, ctx.n_tokens * self.nh, 2), torch.float32)
-            unmerged = ctx.decode_only and 1 < splits <= self.MERGE_IN_PRODUCT_SPLITS and self.nh // self.nkv <= 16 and ctx.n_tokens <= 16
-            ops.attention_bf16(
-                out, q, cache.k, cache.v, ctx.q_start, ctx.kv_len, ctx.positions, group.block_table, group.page_size, ctx.n_seqs, ctx.max_q_len,
-                self.nh, self.nkv, self.hd, self.window, self.scale, splits, per_split, po, pml, longest, ctx.status, combine=not unmerged,
-            )
-            if unmerged:
-                return MergedSplits(po, pml, ctx.positions, ctx.n_tokens, self.nh, self.hd, self.window, per_split, ctx.buf)
-            return out
-        ops.paged_attention_generic(
-            out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size,
-            self.nh, self.nkv, self.hd, self.window, self.scale,
-        )
-        return out
 
 
 register_part("mixer", "gqa_attention", GQAttention)

@@ -20,11 +20,12 @@ import torch
 
 from ..csrc import ops
 from ..errors import AlofaError
+from .attention import PagedAttend
 from .base import PagedKV, Part, TensorSpec, register_part
 from .linear import RESIDUAL, STORE, Linear, add_into_stream
 
 
-class NormedAttention(Part):
+class NormedAttention(PagedAttend, Part):
     family = "mixer"
     graph_safe = True
     stores_output = True
@@ -48,6 +49,7 @@ class NormedAttention(Part):
         if self.every <= 0 or self.softcap < 0:
             raise AlofaError("invalid_argument", "q_temp_every must be positive and softcap not negative", f"params={self.params}")
         self.q_dim, self.k_dim, self.v_dim = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.nh, self.nkv, self.hd = self.heads, self.kv_heads, self.dim  # what the shared choice of kernels goes by (keys and values alike only)
 
     def cache_spec(self):
         return PagedKV(self.kv_heads, self.dim, self.window, self.vdim)
@@ -75,9 +77,12 @@ class NormedAttention(Part):
         self.qkv(sums, x, buf=ctx.buf)
         q = ctx.buf((n, self.q_dim), dt)
         ops.qkv_prepare(q, cache.k, cache.v, sums, ctx.positions, group.slot_map, self.heads, self.kv_heads, self.dim, self.vdim, self.qk_norm, self.eps, self.coef, self.every)
-        out = ctx.buf((n, self.heads * self.vdim), dt)
-        ops.paged_attention_generic(out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size, self.heads, self.kv_heads,
-                                    self.dim, self.window, self.scale, self.softcap, self.vdim)
+        if self.dim == self.vdim:
+            out = self.attend(ctx, q, cache, group)  # the tensor-core kernels in bfloat16 for the head sizes they are built for, else the every-size kernel
+        else:
+            out = ctx.buf((n, self.heads * self.vdim), dt)
+            ops.paged_attention_generic(out, q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, group.block_table, group.page_size, self.heads, self.kv_heads,
+                                        self.dim, self.window, self.scale, self.softcap, self.vdim)
         if store:
             self.out_store(h, out, buf=ctx.buf)
         else:

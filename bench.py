@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--shape 0.5b|1.5b|7b] [--no-extra]
     python bench.py --design kotutar [--size 1k|2k]     (another line: that design beside Qwen2 at equal layer sizes)
+    python bench.py --design darolix [--size 1k|2k]     (another line: that design beside Kotutar at equal layer sizes)
 
 The default run has the layer sizes of the Qwen2.5-0.5B shape with random
 weights, a batch of 8 requests with 2,048-token prompts inside a 4,096-token
@@ -281,7 +282,7 @@ class Bench:
         mean_kv = prompt_len + warmup + steps / 2
         for s in slots:
             runner.release(s)
-        step_bytes = self.numbers["weight_bytes"] + self.numbers["kv_bytes_per_token"] * mean_kv * batch
+        step_bytes = self.numbers["weight_bytes"] + self.numbers["kv_bytes_per_token"] * mean_kv * batch + self.numbers.get("state_bytes_per_request", 0) * batch
         achieved = step_bytes / (ms * 1e-3) / 1e9
         return {"ms": ms, "tok_s": batch / ms * 1e3, "bytes": step_bytes, "launches": launches, "clocks": clock_report, "step_ms": self.spread(each),
                 "gbs": achieved, "frac": achieved / self.peaks["hbm_gbs"]}
@@ -462,6 +463,35 @@ DESIGN_SIZES = {
 }
 
 
+# --design darolix: state-space / attention + linear-attention layers with routed experts, beside the Kotutar design at the
+# same width, layers, heads, experts and expert width.  Inner sizes after published models of the kind: the state-space
+# inner size twice the width in heads of 64 with a state of 128, attention heads of 128, linear attention with keys half and
+# values as wide as the model.
+DAROLIX_SIZES = {
+    "1k": dict(ssm_heads=32, ssm_vdim=64, state=128, groups=1, conv=4, norm_groups=1, kv_heads=2, att_dim=128, gla_heads=4, gla_dim=128, gla_vdim=256, identity=2),
+    "2k": dict(ssm_heads=64, ssm_vdim=64, state=128, groups=1, conv=4, norm_groups=1, kv_heads=4, att_dim=128, gla_heads=8, gla_dim=128, gla_vdim=256, identity=4),
+}
+
+
+def darolix_config(z: dict, d: dict):
+    """State-space and side-by-side layers in turn, every layer with routed experts, no loop."""
+    from alofa_b200.models.darolix import DarolixConfig, DarolixLayer, LeftConfig, MoeConfig, RightConfig, StateSpaceConfig
+
+    ssm = StateSpaceConfig(d["ssm_heads"], d["ssm_vdim"], d["state"], d["groups"], d["conv"], d["norm_groups"])
+    pair = (LeftConfig(z["heads"], d["kv_heads"], d["att_dim"], d["att_dim"], d["att_dim"] ** -0.5, 50.0, 0.3, 128), RightConfig(d["gla_heads"], d["gla_dim"], d["gla_vdim"], 16.0))
+    moe = MoeConfig(z["experts"], z["top"], z["expert_ff"], d["identity"])
+    layers = [DarolixLayer("mamba2", ssm, moe) if i % 2 == 0 else DarolixLayer("parallel", pair, moe) for i in range(z["layers"])]
+    return DarolixConfig(z["vocab"], z["width"], 1e-6, float(z["width"]) ** 0.5, layers)
+
+
+def kotutar_config_routed(z: dict):
+    """The closest existing design at equal size: latent attention and routed experts (no shared one) in every layer."""
+    from alofa_b200.models.kotutar import KotutarConfig, KotutarLayer, LatentMixerConfig, MlpConfig
+
+    mixer = LatentMixerConfig(z["heads"], z["dim"], z["rot"], z["vdim"], z["kv_rank"], z["q_rank"], (z["dim"] + z["rot"]) ** -0.5, 1e4, z["rot"])
+    return KotutarConfig(z["vocab"], z["width"], 1e-6, [KotutarLayer("latent_attention", mixer, MlpConfig("moe", z["expert_ff"], z["experts"], z["top"], 0)) for _ in range(z["layers"])])
+
+
 def kotutar_config(z: dict):
     """Half of the layers dense, half routed, no loop: what a step costs per layer is what is measured."""
     from alofa_b200.models.kotutar import KotutarConfig, KotutarLayer, LatentMixerConfig, MlpConfig
@@ -487,6 +517,7 @@ class KernelClock:
 
     PRODUCTS = ("gemm_tc", "gemm_generic", "gemm_batched", "gemm_tc_rope")
     ATTENTION = ("attention_bf16", "latent_attention_bf16", "latent_attention", "paged_attention_generic")
+    STATE = ("linear_scan", "causal_conv")  # read and leave a state per request
 
     def __init__(self, peaks: dict):
         self.peaks = peaks
@@ -510,6 +541,15 @@ class KernelClock:
             by_tile = kwargs.get("tile_batch") is not None
             flops = 2.0 * m * n * k * (1 if by_tile else batches)
             byts = (out.element_size() * m * n + x.element_size() * m * k) * (1 if by_tile else batches) + w.numel() * w.element_size()
+        elif name == "linear_scan":
+            # y, v, ., b, ., c, ., dec, ., state, q_start, slots, n_seqs, heads, groups, n, p: the rows once, the live requests' states read and written
+            y, n_seqs, heads, groups, n, p = args[0], args[12], args[13], args[14], args[15], args[16]
+            rows = y.shape[0]
+            byts = 4 * rows * (2 * heads * p + 2 * groups * n + (heads * n if args[17] else heads)) + 8 * n_seqs * heads * n * p
+            flops = 0.0  # fp32 arithmetic, none of it on the tensor cores: the state's bytes are the bound
+        elif name == "causal_conv":
+            out = args[0]
+            byts = 8 * out.numel() + 8 * args[9] * (args[3].shape[1] - 1) * out.shape[1]
         elif name in self.ATTENTION:
             # out, q, cache(s): every visible row of the cache is read once per request (bytes) and multiplied by every query row (flops)
             out, q = args[0], args[1]
@@ -568,7 +608,8 @@ class KernelClock:
 class DesignBench(Bench):
     """One engine of one design at one size, measured like the headline bench's."""
 
-    def __init__(self, architecture: str, cfg, label: str, vocab: int, weight_bytes: int, kv_bytes_per_token: int, flops_per_token: float, attn_flops_per_pair: float, max_batch: int):
+    def __init__(self, architecture: str, cfg, label: str, vocab: int, weight_bytes: int, kv_bytes_per_token: int, flops_per_token: float, attn_flops_per_pair: float, max_batch: int,
+                 state_bytes_per_request: int = 0):
         import numpy as np
 
         from alofa_b200.engine.engine import Engine
@@ -578,7 +619,7 @@ class DesignBench(Bench):
         self.engine = Engine.from_random(architecture, cfg, seed=0, dtype="bfloat16", generate_on_device=True, block_size=64, max_batch=max_batch,
                                          max_tokens=CONTEXT, token_budget=PROMPT_LEN + max_batch, max_chunk=PROMPT_LEN)
         self.runner = self.engine.runner
-        self.numbers = {"weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token}
+        self.numbers = {"weight_bytes": weight_bytes, "kv_bytes_per_token": kv_bytes_per_token, "state_bytes_per_request": state_bytes_per_request}
         self.flops_per_token, self.attn_flops_per_pair = flops_per_token, attn_flops_per_pair
         self.peaks, self.peaks_kind = peaks()
         self.rng = np.random.default_rng(0)
@@ -631,7 +672,7 @@ class DesignBench(Bench):
         return {"prefill_2048": prefill[:8], f"decode_b{batch}": decode[:8]}
 
 
-def design_numbers(design: str, z: dict) -> dict:
+def design_numbers(design: str, z: dict, routed_only: bool = False) -> dict:
     """Bytes a decode step reads and flops a token costs, from the sizes (bf16)."""
     w, h = z["width"], z["heads"]
     if design == "kotutar":
@@ -641,6 +682,8 @@ def design_numbers(design: str, z: dict) -> dict:
         expert = 2 * w * z["expert_ff"]
         shared = 2 * w * z["shared_ff"]
         n_dense, n_moe = (z["layers"] + 1) // 2, z["layers"] // 2
+        if routed_only:  # every layer routed, no shared expert
+            n_dense, n_moe, shared = 0, z["layers"], 0
         params_all = z["layers"] * mixer + n_dense * dense + n_moe * (z["experts"] * expert + shared + (z["experts"] + 1) * w)
         per_token = z["layers"] * mixer + n_dense * dense + n_moe * (z["top"] * expert + shared + (z["experts"] + 1) * w)
         return {"weight_bytes": 2 * (params_all + z["vocab"] * w), "kv_bytes_per_token": z["layers"] * d_row * 2, "flops_per_token": 2.0 * per_token,
@@ -651,19 +694,43 @@ def design_numbers(design: str, z: dict) -> dict:
             "attn_flops_per_pair": z["layers"] * 4.0 * h * hd, "head_flops": 2.0 * w * z["vocab"]}
 
 
-def run_designs(args) -> dict:
-    """Prefill and decode of the latent-attention design beside the Qwen2 design at equal layer sizes,
-    and the kernels of one step of each against their own rooflines."""
-    from alofa_b200.models import kotutar, qwen2
+def darolix_numbers(z: dict, d: dict) -> dict:
+    """Bytes a decode step reads and flops a token costs for the Darolix sizes (bf16 weights, fp32 states)."""
+    w = z["width"]
+    inner, bc = d["ssm_heads"] * d["ssm_vdim"], d["groups"] * d["state"]
+    ssm = w * (2 * inner + 2 * bc + d["ssm_heads"]) + inner * w
+    att = w * (z["heads"] + 2 * d["kv_heads"]) * d["att_dim"] + z["heads"] * d["att_dim"] * w
+    qk, v = d["gla_heads"] * d["gla_dim"], d["gla_heads"] * d["gla_vdim"]
+    gla = w * (2 * qk + 2 * v) + v * w + 16 * (w + qk)
+    expert = 3 * w * z["expert_ff"]
+    router = (z["experts"] + d["identity"]) * w
+    n_ssm, n_pair = (z["layers"] + 1) // 2, z["layers"] // 2
+    params_all = n_ssm * ssm + n_pair * (att + gla) + z["layers"] * (z["experts"] * expert + router)
+    per_token = n_ssm * ssm + n_pair * (att + gla) + z["layers"] * (z["top"] * expert + router)
+    state_bytes = 4 * (n_ssm * (inner * d["state"] + (d["conv"] - 1) * (inner + 2 * bc)) + n_pair * qk * d["gla_vdim"])
+    return {"weight_bytes": 2 * (params_all + 2 * z["vocab"] * w), "kv_bytes_per_token": n_pair * 2 * d["kv_heads"] * d["att_dim"] * 2, "flops_per_token": 2.0 * per_token,
+            "attn_flops_per_pair": n_pair * 4.0 * z["heads"] * d["att_dim"], "head_flops": 2.0 * w * z["vocab"], "state_bytes_per_request": 2 * state_bytes}
 
-    out = {"metric": "prefill and decode of the Kotutar design beside Qwen2 at equal layer sizes", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+
+def run_designs(args) -> dict:
+    """Prefill and decode of a design beside its closest existing design at equal layer sizes (Kotutar
+    beside Qwen2, Darolix beside Kotutar), and the kernels of one step of each against their own rooflines."""
+    from alofa_b200.models import darolix, kotutar, qwen2
+
+    pair = "Darolix design beside Kotutar" if args.design == "darolix" else "Kotutar design beside Qwen2"
+    out = {"metric": f"prefill and decode of the {pair} at equal layer sizes", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
            "prompt_tokens": PROMPT_LEN, "context": CONTEXT, "steps": args.steps, "warmup": args.warmup, "sizes": {}}
     for size in ([args.size] if args.size else sorted(DESIGN_SIZES)):
         z = DESIGN_SIZES[size]
         row = {"sizes": z}
-        for design, name, cfg in (("kotutar", kotutar.NAME, kotutar_config(z)), ("qwen2", qwen2.NAME, qwen2_config_like(z))):
-            n = design_numbers(design, z)
-            bench = DesignBench(name, cfg, f"{design} {size}", z["vocab"], n["weight_bytes"], n["kv_bytes_per_token"], n["flops_per_token"], n["attn_flops_per_pair"], 64)
+        if args.design == "darolix":
+            row["darolix_sizes"] = DAROLIX_SIZES[size]
+            arms = (("darolix", darolix.NAME, darolix_config(z, DAROLIX_SIZES[size])), ("kotutar", kotutar.NAME, kotutar_config_routed(z)))
+        else:
+            arms = (("kotutar", kotutar.NAME, kotutar_config(z)), ("qwen2", qwen2.NAME, qwen2_config_like(z)))
+        for design, name, cfg in arms:
+            n = darolix_numbers(z, DAROLIX_SIZES[size]) if design == "darolix" else design_numbers(design, z, routed_only=args.design == "darolix")
+            bench = DesignBench(name, cfg, f"{design} {size}", z["vocab"], n["weight_bytes"], n["kv_bytes_per_token"], n["flops_per_token"], n["attn_flops_per_pair"], 64, n.get("state_bytes_per_request", 0))
             res = {"prefill_2048": bench.prefill(args.warmup)}
             for batch in (8, 64):
                 point = bench.decode(batch, min(args.steps, 64), args.warmup)
@@ -693,7 +760,7 @@ def main() -> int:
     ap.add_argument("--phase", choices=["all", "decode", "prefill"], default="all", help="profiling aid: run only one part; the JSON line then lacks the others")
     ap.add_argument("--shape", choices=sorted(SHAPES), default="0.5b", help="whose layer sizes the headline run has")
     ap.add_argument("--no-extra", dest="extra", action="store_false", help="leave out the measurements beside the headline (long contexts, the 1.5B and 7B shapes)")
-    ap.add_argument("--design", choices=["kotutar"], help="instead of the headline run: this design beside Qwen2 at equal layer sizes (prefill, decode, kernels against their rooflines)")
+    ap.add_argument("--design", choices=["kotutar", "darolix"], help="instead of the headline run: this design beside its closest existing one (Qwen2 for kotutar, Kotutar for darolix) at equal layer sizes (prefill, decode, kernels against their rooflines)")
     ap.add_argument("--size", choices=sorted(DESIGN_SIZES), help="with --design: one of the sizes only")
     args = ap.parse_args()
     if args.impl == "reference":
