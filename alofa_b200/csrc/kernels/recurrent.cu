@@ -123,200 +123,304 @@ ALOFA_API int alofa_causal_conv(float* out, const float* u, int ld, int offset, 
 }
 
 // ---------------------------------------------------------------------------
-// The recurrence.  One block takes one (request, head) and a range of value channels and walks the
-// request's tokens of this step in order.  A thread holds R consecutive key channels of one value
-// channel of the state in registers (the state lies in memory as [head][value channel][key
-// channel]); the NS threads that share a value channel are neighbours in a warp and add their
-// shares of y in butterfly order.  Keys, queries, decays and values of TC tokens at a time are
-// staged in shared memory, where the decays are made: softplus, exponentials and the logarithm of
-// the sigmoid are the precise fp32 library functions.
+// The recurrence, in two kernels.
 //
-//   mode 0 (one decay per head and token): dt = softplus(dec[t, h] + dt_bias[h]),
-//          a = exp(-exp(A_log[h]) * dt), k = dt * b[t, g, :], q = c[t, g, :], y += D[h] * v
-//   mode 1 (one decay per key channel):    a[n] = exp(log_sigmoid(dec[t, h, n]) * tau_inv),
-//          k = b[t, h, :], q = c[t, h, :] * q_scale
-// with g = h / (H / G) the group of head h.
+// scan_decays: what the recurrence multiplies by, once per token, in fp32 with the precise library functions:
+//   mode 0 (one decay per head and token): dt = softplus(dec[t, h] + dt_bias[h]) and a = exp(-exp(A_log[h]) * dt)
+//   mode 1 (one decay per key channel):    a[n] = exp(log_sigmoid(dec[t, h, n]) / tau) = sigmoid(.)^(1/tau)
+//
+// linear_scan: one block takes one (request, head) and a range of value channels and walks the
+// request's tokens of this step in order.  A thread holds, for two value channels, 4 * J key
+// channels of the state in registers (the state lies in memory as [head][value channel][key
+// channel]; a thread's key channels are the 16-byte groups ns, ns + NS, ...).  The NS threads that
+// share value channels are neighbours in a warp and add their shares of y in butterfly order, four
+// tokens' sums at a time so that the exchanges of one token overlap the arithmetic of the next.
+// Keys, queries, decays and values of 16 tokens at a time (fewer for very wide keys) come into shared
+// memory by asynchronous copies, the next ones while these are worked on.
+//
+//   mode 0: k_t = dt_t * b[t, g, :], q_t = c[t, g, :], y_t += D[h] * v_t      (g = h / (H / G))
+//   mode 1: k_t = b[t, h, :],        q_t = c[t, h, :] * q_scale
 // ---------------------------------------------------------------------------
+__global__ void scan_decays_kernel(float* __restrict__ a_out, float* __restrict__ dt_out, const float* __restrict__ dec, int ldd, int d_off,
+                                   const float* __restrict__ dt_bias, const float* __restrict__ A_log, float tau_inv, long long count, int cols, int mode) {
+  pdl_begin();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const long long t = i / cols;
+  const int c = (int)(i - t * cols);
+  const float z = dec[t * ldd + d_off + c];
+  if (mode == 0) {
+    const float dt = softplus_f(z + (dt_bias ? dt_bias[c] : 0.f));
+    dt_out[i] = dt;
+    a_out[i] = expf(-expf(A_log[c]) * dt);
+  } else {
+    a_out[i] = expf(-softplus_f(-z) * tau_inv);
+  }
+}
+
 struct ScanArgs {
-  float* y;            // [T, H * P]
-  const float* v; int ldv, v_off;      // values:  v[t * ldv + v_off + h * P + p]
-  const float* b; int ldb, b_off;      // keys:    b[t * ldb + b_off + g * N + n]
-  const float* c; int ldc, c_off;      // queries: c[t * ldc + c_off + g * N + n]
-  const float* dec; int ldd, d_off;    // decay inputs: mode 0 [t, h], mode 1 [t, h * N + n]
-  const float* dt_bias; const float* A_log; const float* D;
-  float tau_inv, q_scale;
+  float* y;                             // [T, H * P]
+  const float* v; int ldv, v_off;       // values:  v[t * ldv + v_off + h * P + p]
+  const float* k; int ldk, k_off;       // keys:    k[t * ldk + k_off + g * N + n]
+  const float* q; int ldq, q_off;       // queries: q[t * ldq + q_off + g * N + n]
+  const float* a;                       // decays: mode 0 [T, H], mode 1 [T, H * N]
+  const float* dt;                      // mode 0: step sizes [T, H]
+  const float* D;
+  float q_scale;
   float* state; long long slot_stride;  // state of slot s at state + s * slot_stride, [H][P][N]
   const int* q_start; const int* state_slots;
-  int H, G, N, P, mode, NS, PC;
+  int H, G, N, P, NS, PC, vec, TC;      // vec: every row and offset is a multiple of 4 floats (16-byte copies); TC: tokens a stage holds
 };
 
-constexpr int SCAN_TC = 16;
 
-template <int R>
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_done() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <int J, int MODE>
 __global__ void __launch_bounds__(512) linear_scan_kernel(const ScanArgs a) {
-  extern __shared__ float scan_smem[];
+  extern __shared__ __align__(16) float scan_smem[];
+  constexpr int R = 4 * J;
   const int N = a.N, P = a.P, NS = a.NS, PC = a.PC;
-  const int NP = N + (N >> 5) + 1;  // padded rows: threads R apart do not meet in one bank
-  float* ks = scan_smem;                  // [TC][NP]
-  float* qs = ks + SCAN_TC * NP;          // [TC][NP]
-  float* as = qs + SCAN_TC * NP;          // [TC][NP] (mode 1) or [TC] (mode 0)
-  float* vs = as + (a.mode ? SCAN_TC * NP : SCAN_TC);  // [TC][PC]
-  pdl_begin();
+  const int NW = NS * R;  // key channels a stage holds per token (zeros past N)
+  const int SCAN_TC = a.TC;
+  const int per_stage = SCAN_TC * (2 * NW + (MODE ? NW : 2) + PC);
   const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * PC;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int pl = tid / NS, ns = tid - pl * NS;
-  const int p = p0 + pl;
-  const bool active = pl < PC && p < P;
+  const int pa = p0 + 2 * pl, pb = pa + 1;
+  const bool in_a = 2 * pl < PC && pa < P, in_b = 2 * pl + 1 < PC && pb < P;
   const int g = h / (a.H / a.G);
+  // the tails of the rows that no copy writes stay zero: keys and queries of zero leave state and sums alone
+  for (int e = tid; e < 2 * per_stage; e += nthreads) scan_smem[e] = 0.f;
+  pdl_begin();
   const int t0 = a.q_start[s], t1 = a.q_start[s + 1];
-  float* S = a.state + (long long)a.state_slots[s] * a.slot_stride + ((size_t)h * P + (active ? p : 0)) * N;
-  const int n0 = ns * R;
-  float st[R];
+  float* S = a.state + (long long)a.state_slots[s] * a.slot_stride + (size_t)h * P * N;
+  float sa[R], sb[R];
 #pragma unroll
-  for (int i = 0; i < R; ++i) st[i] = (active && n0 + i < N) ? S[n0 + i] : 0.f;
-  const float dskip = (a.mode == 0 && a.D) ? a.D[h] : 0.f;
-  const float rate = a.mode == 0 ? expf(a.A_log[h]) : 0.f;
-  const float dtb = (a.mode == 0 && a.dt_bias) ? a.dt_bias[h] : 0.f;
-  for (int c0 = t0; c0 < t1; c0 += SCAN_TC) {
+  for (int j = 0; j < J; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = (j * NS + ns) * 4 + e;
+      sa[j * 4 + e] = (in_a && n < N) ? S[(size_t)pa * N + n] : 0.f;
+      sb[j * 4 + e] = (in_b && n < N) ? S[(size_t)pb * N + n] : 0.f;
+    }
+  const float dskip = (MODE == 0 && a.D) ? a.D[h] : 0.f;
+  __syncthreads();
+
+  auto stage_at = [&](int which) { return scan_smem + which * per_stage; };
+  auto fetch = [&](int which, int c0) {
+    float* ks = stage_at(which);
+    float* qs = ks + SCAN_TC * NW;
+    float* as = qs + SCAN_TC * NW;
+    float* vs = as + SCAN_TC * (MODE ? NW : 2);
     const int live = min(SCAN_TC, t1 - c0);
-    __syncthreads();
-    if (a.mode == 0) {
-      for (int tt = tid; tt < live; tt += nthreads) as[tt] = softplus_f(a.dec[(size_t)(c0 + tt) * a.ldd + a.d_off + h] + dtb);
-      __syncthreads();
-    }
-    for (int e = tid; e < live * N; e += nthreads) {
-      const int tt = e / N, n = e - tt * N;
-      const size_t t = c0 + tt;
-      const int at = tt * NP + n + (n >> 5);
-      const float kv = a.b[t * a.ldb + a.b_off + g * N + n];
-      qs[at] = a.c[t * a.ldc + a.c_off + g * N + n] * a.q_scale;
-      if (a.mode == 0) {
-        ks[at] = as[tt] * kv;
-      } else {
-        ks[at] = kv;
-        const float z = a.dec[t * a.ldd + a.d_off + h * N + n];
-        as[at] = expf(-softplus_f(-z) * a.tau_inv);  // sigmoid(z)^(1/tau) through its logarithm
+    if (a.vec) {
+      const int n4 = N >> 2;
+      for (int e = tid; e < live * n4; e += nthreads) {
+        const int tt = e / n4, c = (e - tt * n4) * 4;
+        const size_t t = c0 + tt;
+        cp_async_16(ks + tt * NW + c, a.k + t * a.ldk + a.k_off + g * N + c);
+        cp_async_16(qs + tt * NW + c, a.q + t * a.ldq + a.q_off + g * N + c);
+        if (MODE) cp_async_16(as + tt * NW + c, a.a + t * ((size_t)a.H * N) + h * N + c);
+      }
+      const int p4 = PC >> 2;
+      for (int e = tid; e < live * p4; e += nthreads) {
+        const int tt = e / p4, c = (e - tt * p4) * 4;
+        if (p0 + c < P) cp_async_16(vs + tt * PC + c, a.v + (size_t)(c0 + tt) * a.ldv + a.v_off + h * P + p0 + c);
+      }
+    } else {
+      for (int e = tid; e < live * N; e += nthreads) {
+        const int tt = e / N, c = e - tt * N;
+        const size_t t = c0 + tt;
+        cp_async_4(ks + tt * NW + c, a.k + t * a.ldk + a.k_off + g * N + c);
+        cp_async_4(qs + tt * NW + c, a.q + t * a.ldq + a.q_off + g * N + c);
+        if (MODE) cp_async_4(as + tt * NW + c, a.a + t * ((size_t)a.H * N) + h * N + c);
+      }
+      for (int e = tid; e < live * PC; e += nthreads) {
+        const int tt = e / PC, c = e - tt * PC;
+        if (p0 + c < P) cp_async_4(vs + tt * PC + c, a.v + (size_t)(c0 + tt) * a.ldv + a.v_off + h * P + p0 + c);
       }
     }
-    for (int e = tid; e < live * PC; e += nthreads) {
-      const int tt = e / PC, q = e - tt * PC;
-      vs[e] = p0 + q < P ? a.v[(size_t)(c0 + tt) * a.ldv + a.v_off + h * P + p0 + q] : 0.f;
-    }
-    __syncthreads();
-    for (int tt = 0; tt < live; ++tt) {
-      const float xv = pl < PC ? vs[tt * PC + pl] : 0.f;
-      const float* kr = ks + tt * NP;
-      const float* qr = qs + tt * NP;
-      float acc = 0.f;
-      if (a.mode == 0) {
-        const float dec = expf(-rate * as[tt]);
+    if (!MODE)
+      for (int tt = tid; tt < live; tt += nthreads) {
+        cp_async_4(as + 2 * tt, a.a + (size_t)(c0 + tt) * a.H + h);
+        cp_async_4(as + 2 * tt + 1, a.dt + (size_t)(c0 + tt) * a.H + h);
+      }
+  };
+
+  if (t0 < t1) fetch(0, t0);
+  int which = 0;
+  for (int c0 = t0; c0 < t1; c0 += SCAN_TC, which ^= 1) {
+    cp_async_done();
+    __syncthreads();  // this stage has arrived for everyone, and everyone is done with the other
+    if (c0 + SCAN_TC < t1) fetch(which ^ 1, c0 + SCAN_TC);
+    const int live = min(SCAN_TC, t1 - c0);
+    const float* ks = stage_at(which);
+    const float* qs = ks + SCAN_TC * NW;
+    const float* as = qs + SCAN_TC * NW;
+    const float* vs = as + SCAN_TC * (MODE ? NW : 2);
+    for (int tt0 = 0; tt0 < live; tt0 += 4) {
+      float ya[4], yb[4], xa[4], xb[4];
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int n = n0 + i, at = n + (n >> 5);
-          if (n < N) {
-            st[i] = fmaf(dec, st[i], kr[at] * xv);
-            acc = fmaf(st[i], qr[at], acc);
+      for (int u = 0; u < 4; ++u) {
+        const int tt = tt0 + u;
+        ya[u] = yb[u] = xa[u] = xb[u] = 0.f;
+        if (tt < live) {
+          xa[u] = 2 * pl < PC ? vs[tt * PC + 2 * pl] : 0.f;
+          xb[u] = 2 * pl + 1 < PC ? vs[tt * PC + 2 * pl + 1] : 0.f;
+          float dec = 0.f, ka = xa[u], kb = xb[u];
+          if (MODE == 0) {
+            dec = as[2 * tt];
+            ka *= as[2 * tt + 1];
+            kb *= as[2 * tt + 1];
           }
-        }
-      } else {
-        const float* ar = as + tt * NP;
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          const int n = n0 + i, at = n + (n >> 5);
-          if (n < N) {
-            st[i] = fmaf(ar[at], st[i], kr[at] * xv);
-            acc = fmaf(st[i], qr[at], acc);
+          for (int j = 0; j < J; ++j) {
+            const int at = tt * NW + (j * NS + ns) * 4;
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + at);
+            float4 a4 = make_float4(dec, dec, dec, dec);
+            if (MODE) a4 = *reinterpret_cast<const float4*>(as + at);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              sa[j * 4 + e] = fmaf(aa[e], sa[j * 4 + e], kk[e] * ka);
+              sb[j * 4 + e] = fmaf(aa[e], sb[j * 4 + e], kk[e] * kb);
+              ya[u] = fmaf(sa[j * 4 + e], qq[e], ya[u]);
+              yb[u] = fmaf(sb[j * 4 + e], qq[e], yb[u]);
+            }
           }
         }
       }
-      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (active && ns == 0) a.y[(size_t)(c0 + tt) * a.H * P + h * P + p] = acc + dskip * xv;
+      for (int o = NS >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          ya[u] += __shfl_xor_sync(0xffffffffu, ya[u], o);
+          yb[u] += __shfl_xor_sync(0xffffffffu, yb[u], o);
+        }
+      }
+      if (ns == 0) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (tt0 + u < live) {
+            float* yr = a.y + (size_t)(c0 + tt0 + u) * a.H * P + h * P;
+            if (in_a) yr[pa] = ya[u] * a.q_scale + dskip * xa[u];
+            if (in_b) yr[pb] = yb[u] * a.q_scale + dskip * xb[u];
+          }
+        }
+      }
     }
   }
-  if (active) {
 #pragma unroll
-    for (int i = 0; i < R; ++i)
-      if (n0 + i < N) S[n0 + i] = st[i];
-  }
+  for (int j = 0; j < J; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int n = (j * NS + ns) * 4 + e;
+      if (in_a && n < N) S[(size_t)pa * N + n] = sa[j * 4 + e];
+      if (in_b && n < N) S[(size_t)pb * N + n] = sb[j * 4 + e];
+    }
 }
 
-template <int R>
+template <int J, int MODE>
 static int linear_scan_launch(const ScanArgs& a, int n_seqs, int threads, size_t smem, cudaStream_t stream) {
   static size_t set = 48 * 1024;
   if (smem > set) {
-    if (cudaFuncSetAttribute(linear_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(linear_scan_kernel<J, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
     set = smem;
   }
-  launch_dep(linear_scan_kernel<R>, dim3(a.H, n_seqs, (a.P + a.PC - 1) / a.PC), threads, smem, stream, a);
+  launch_dep(linear_scan_kernel<J, MODE>, dim3(a.H, n_seqs, (a.P + a.PC - 1) / a.PC), threads, smem, stream, a);
   return launch_status();
 }
 
-// `spread`: how many blocks the launch should have at least, if the value channels allow it (a
-// prompt of one request has few (request, head) pairs; its value channels are dealt to more blocks).
+// work: fp32 scratch of n_tokens * (mode 0: 2 * H; mode 1: H * N) numbers for the decays.  spread: how many blocks the scan
+// should have at least, if the value channels allow it (a prompt of one request has few (request, head) pairs; its value
+// channels are dealt to more blocks).
 ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, const float* b, int ldb, int b_off, const float* c, int ldc, int c_off,
                                 const float* dec, int ldd, int d_off, const float* dt_bias, const float* A_log, const float* D, float tau_inv, float q_scale,
-                                float* state, long long slot_stride, const int* q_start, const int* state_slots, int n_seqs, int H, int G, int N, int P,
-                                int mode, int spread, cudaStream_t stream) {
-  if (n_seqs <= 0) return ALOFA_OK;
-  if (H <= 0 || G <= 0 || H % G || N <= 0 || N > 1024 || P <= 0 || (mode == 0 && !A_log)) return ALOFA_ERR_ARGUMENT;
-  const int R = N <= 256 ? 8 : (N <= 512 ? 16 : 32);
+                                float* state, long long slot_stride, const int* q_start, const int* state_slots, int n_tokens, int n_seqs, int H, int G, int N,
+                                int P, int mode, int spread, float* work, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
+  if (H <= 0 || G <= 0 || H % G || N <= 0 || N > 1024 || P <= 0 || !work || (mode == 0 && !A_log)) return ALOFA_ERR_ARGUMENT;
+  const int cols = mode ? H * N : H;
+  const long long count = (long long)n_tokens * cols;
+  float* a_out = work;
+  float* dt_out = mode ? nullptr : work + count;
+  launch_dep(scan_decays_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, a_out, dt_out, dec, ldd, d_off, dt_bias, A_log, tau_inv, count, cols, mode);
+  // key channels a thread holds (4 * J): 16 measured best from 128 key channels on, for prompts (0.65 ms for 2,048 tokens of 32 heads
+  // of 128 x 64 against 0.67 with 8) and for decode steps (53 us for 64 requests against 86)
+  const int J = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 512 ? 4 : 8));
+  const int R = 4 * J;
   int NS = 1;
   while (NS * R < N) NS *= 2;
-  int PC = 512 / NS;  // value channels per block
-  if (PC > P) PC = P;
-  while (PC > 8 && (long long)H * n_seqs * ((P + PC - 1) / PC) < spread) PC = (PC + 1) / 2;
-  const int threads = (PC * NS + 31) / 32 * 32;
-  ScanArgs a = {y, v, ldv, v_off, b, ldb, b_off, c, ldc, c_off, dec, ldd, d_off, dt_bias, A_log, D, tau_inv, q_scale, state, slot_stride, q_start, state_slots,
-                H, G, N, P, mode, NS, PC};
-  const int NP = N + (N >> 5) + 1;
-  const size_t smem = ((size_t)SCAN_TC * NP * (mode ? 3 : 2) + (mode ? 0 : SCAN_TC) + (size_t)SCAN_TC * PC) * sizeof(float);
+  if (NS > 32) return ALOFA_ERR_ARGUMENT;
+  const bool vec = N % 4 == 0 && ldv % 4 == 0 && v_off % 4 == 0 && P % 4 == 0 && ldb % 4 == 0 && b_off % 4 == 0 && ldc % 4 == 0 && c_off % 4 == 0 &&
+                   ((uintptr_t)v % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)work % 16 == 0);
+  int PC = 2 * (512 / NS);  // value channels per block: two a thread
+  while (PC > 4 && PC / 2 >= P) PC /= 2;
+  if (PC > 32) PC = 32;  // more blocks of fewer warps: measured best at 32 value channels a block for prompts and decode steps alike
+  while (PC > 8 && (long long)H * n_seqs * ((P + PC - 1) / PC) < spread) PC /= 2;
+  if (PC < 4) PC = 4;
+  const int threads = ((PC / 2) * NS + 31) / 32 * 32;
+  int TC = 16;  // tokens a stage holds: fewer when the keys are so wide that two stages of 16 do not fit
+  while (TC > 4 && (size_t)2 * TC * (2 * NS * R + (mode ? NS * R : 2) + PC) * sizeof(float) > 160 * 1024) TC /= 2;
+  ScanArgs a = {y, v, ldv, v_off, b, ldb, b_off, c, ldc, c_off, a_out, dt_out, D, q_scale, state, slot_stride, q_start, state_slots, H, G, N, P, NS, PC, vec ? 1 : 0, TC};
+  const size_t smem = (size_t)2 * TC * (2 * NS * R + (mode ? NS * R : 2) + PC) * sizeof(float);
   if (smem > 200 * 1024) return ALOFA_ERR_ARGUMENT;
-  if (R == 8) return linear_scan_launch<8>(a, n_seqs, threads, smem, stream);
-  if (R == 16) return linear_scan_launch<16>(a, n_seqs, threads, smem, stream);
-  return linear_scan_launch<32>(a, n_seqs, threads, smem, stream);
+#define SCAN_CASE(JJ) \
+  if (J == JJ) return mode ? linear_scan_launch<JJ, 1>(a, n_seqs, threads, smem, stream) : linear_scan_launch<JJ, 0>(a, n_seqs, threads, smem, stream);
+  SCAN_CASE(1) SCAN_CASE(2) SCAN_CASE(4) SCAN_CASE(8)
+#undef SCAN_CASE
+  return ALOFA_ERR_ARGUMENT;
 }
 
 // ---------------------------------------------------------------------------
 // The norm such a mixer ends with: rows y [T, width] in `groups` equal parts, each part divided by
 // its own root mean square (eps inside the root), times w[c % wlen], and a gate silu(g[t, c]) that
 // multiplies either before the norm (gate_first: the gated values are what is normed) or after it.
-// One block per token, a warp per part in turn.
+// One block per (token, part): as many threads as the part has groups of four numbers, up to 256.
 // ---------------------------------------------------------------------------
 template <typename TO>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ gate, int ldg,
                                                                int g_off, const float* __restrict__ w, int wlen, int width, int groups, float eps,
                                                                int gate_first) {
+  __shared__ float scratch[32];
   pdl_begin();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int part = width / groups;
+  const int t = blockIdx.x, grp = blockIdx.y;
+  const int part = width / groups, lo = grp * part;
   const float* yr = y + (size_t)t * width;
   const float* gr = gate ? gate + (size_t)t * ldg + g_off : nullptr;
-  for (int grp = warp; grp < groups; grp += 8) {
-    const int lo = grp * part;
-    float ss = 0.f;
-    for (int c = lo + lane; c < lo + part; c += 32) {
-      float v = yr[c];
-      if (gr && gate_first) v *= silu_f(gr[c]);
-      ss = fmaf(v, v, ss);
-    }
-    ss = warp_sum(ss);
-    const float r = 1.0f / sqrtf(ss / (float)part + eps);
-    for (int c = lo + lane; c < lo + part; c += 32) {
-      float v = yr[c];
-      if (gr && gate_first) v *= silu_f(gr[c]);
-      v = v * r * w[c % wlen];
-      if (gr && !gate_first) v *= silu_f(gr[c]);
-      out[(size_t)t * width + c] = from_f<TO>(v);
-    }
+  float ss = 0.f;
+  for (int c = lo + threadIdx.x; c < lo + part; c += blockDim.x) {
+    float v = yr[c];
+    if (gr && gate_first) v *= silu_f(gr[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)part + eps);
+  for (int c = lo + threadIdx.x; c < lo + part; c += blockDim.x) {
+    float v = yr[c];
+    if (gr) v *= silu_f(gr[c]);  // before or after the norm, the gate is a factor of the result
+    out[(size_t)t * width + c] = from_f<TO>(v * r * w[c % wlen]);
   }
 }
 
 ALOFA_API int alofa_gated_group_norm(void* out, const float* y, const float* gate, int ldg, int g_off, const float* w, int wlen, int n_tokens, int width,
                                      int groups, float eps, int gate_first, int out_bf16, cudaStream_t stream) {
   if (n_tokens <= 0) return ALOFA_OK;
-  if (groups <= 0 || width % groups || wlen <= 0) return ALOFA_ERR_ARGUMENT;
-  if (out_bf16) launch_dep(gated_group_norm_kernel<bf16>, n_tokens, 256, 0, stream, (bf16*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
-  else launch_dep(gated_group_norm_kernel<float>, n_tokens, 256, 0, stream, (float*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
+  if (groups <= 0 || groups > 65535 || width % groups || wlen <= 0) return ALOFA_ERR_ARGUMENT;
+  const int part = width / groups;
+  const int threads = part >= 1024 ? 256 : (part >= 256 ? 128 : (part >= 64 ? 64 : 32));
+  const dim3 grid(n_tokens, groups);
+  if (out_bf16) launch_dep(gated_group_norm_kernel<bf16>, grid, threads, 0, stream, (bf16*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
+  else launch_dep(gated_group_norm_kernel<float>, grid, threads, 0, stream, (float*)out, y, gate, ldg, g_off, w, wlen, width, groups, eps, gate_first);
   return launch_status();
 }
 

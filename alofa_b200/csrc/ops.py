@@ -862,7 +862,7 @@ def _recurrent():
             "alofa_embed_scaled": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
             "alofa_add_rows": [_P, _P, _L, _P],
             "alofa_causal_conv": [_P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
-            "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+            "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
             "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
@@ -926,7 +926,7 @@ def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_o
 
 
 def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int, state, q_start, state_slots, n_seqs: int, heads: int, groups: int, n: int, p: int,
-                mode: int, dt_bias=None, a_log=None, d_skip=None, tau: float = 1.0, q_scale: float = 1.0, spread: int = 0) -> None:
+                mode: int, dt_bias=None, a_log=None, d_skip=None, tau: float = 1.0, q_scale: float = 1.0, spread: int = 0, work=None) -> None:
     """The recurrence ``S_t = diag(a_t) S_(t-1) + k_t v_t^T, y_t = S_t^T q_t``
     per head over each request's tokens of the step in order, all fp32; the
     state [slots, >= heads * p * n] (per head [p][n]) is read and left up to
@@ -936,7 +936,8 @@ def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int,
     exp(-exp(a_log[h]) dt)``, keys times dt, ``y += d_skip[h] v``, keys and
     queries shared by the heads of a group.  ``mode`` 1: one decay per key
     channel, ``a = sigmoid(dec[t, h, :]) ** (1 / tau)``, queries times
-    ``q_scale``."""
+    ``q_scale``.  ``work``: fp32 scratch for the decays, :func:`linear_scan_work`
+    numbers (allocated when absent: callers inside a step pass step scratch)."""
     f32, i32 = torch.float32, torch.int32
     rows = y.shape[0]
     if tuple(y.shape) != (rows, heads * p) or state.stride(0) < heads * p * n or state.dtype != f32 or not state.is_cuda:
@@ -945,14 +946,25 @@ def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int,
         if t_.shape[0] != rows or t_.dtype != f32 or t_.dim() != 2:
             raise AlofaError("invalid_argument", "linear_scan operand must be fp32 with one row per token", name)
     opt = lambda t_, name: _dev(t_, name, f32) if t_ is not None else None
+    need = linear_scan_work(rows, heads, n, mode)
+    if work is None:
+        work = torch.empty((need,), dtype=f32, device=y.device)
+    if work.numel() < need:
+        raise AlofaError("invalid_argument", "linear_scan scratch is too small", f"have={work.numel()} need={need}")
+    count_launches(1)  # the kernel that makes the decays
     _done(
         _recurrent().alofa_linear_scan(
             _dev(y, "y", f32), _dev(v, "v"), v.shape[1], v_off, _dev(b, "b"), b.shape[1], b_off, _dev(c, "c"), c.shape[1], c_off, _dev(dec, "dec"), dec.shape[1], d_off,
             opt(dt_bias, "dt_bias"), opt(a_log, "a_log"), opt(d_skip, "d_skip"), 1.0 / float(tau), float(q_scale), state.data_ptr(), state.stride(0),
-            _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), n_seqs, heads, groups, n, p, mode, spread, _stream(),
+            _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), rows, n_seqs, heads, groups, n, p, mode, spread, _dev(work, "work", f32), _stream(),
         ),
         "linear_scan", f"heads={heads} groups={groups} n={n} p={p} mode={mode}",
     )
+
+
+def linear_scan_work(rows: int, heads: int, n: int, mode: int) -> int:
+    """How many fp32 numbers of scratch :func:`linear_scan` needs."""
+    return rows * (heads * n if mode else 2 * heads)
 
 
 def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_first: bool) -> None:

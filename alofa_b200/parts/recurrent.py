@@ -32,8 +32,8 @@ from ..errors import AlofaError
 from .base import Part, SlotState, TensorSpec, as_float32_vector, register_part
 from .linear import RESIDUAL, STORE, Linear, add_into_stream
 
-# blocks a scan launch should have before its value channels stop being dealt to more of them
-SCAN_SPREAD = 296
+# blocks a scan launch should have before its value channels stop being dealt to more of them (about one per SM)
+SCAN_SPREAD = 128
 
 
 def _project_out(ctx, linear_add: Linear, linear_store: Linear, h, x, store: bool) -> None:
@@ -70,7 +70,7 @@ class StateSpaceMixer(Part):
         return SlotState((self.scan_words + self.conv_words,), torch.float32)
 
     def scratch_row_bytes(self) -> int:
-        return 4 * (self.in_rows + self.channels + 2 * self.inner) + 8 * self.hidden
+        return 4 * (self.in_rows + self.channels + 2 * self.inner + 2 * self.heads) + 8 * self.hidden
 
     def tensors(self):
         pre = self.prefix
@@ -106,8 +106,9 @@ class StateSpaceMixer(Part):
         xbc = ctx.buf((n, self.channels), f32)
         ops.causal_conv(xbc, u, inner, self.conv_w, self.conv_b, st[:, self.scan_words:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs)
         y = ctx.buf((n, inner), f32)
+        work = ctx.buf((ops.linear_scan_work(n, self.heads, self.state, 0),), f32)
         ops.linear_scan(y, xbc, 0, xbc, inner, xbc, inner + bc, u, 2 * inner + 2 * bc, st, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.groups,
-                        self.state, self.vdim, 0, dt_bias=self.dt_bias, a_log=self.a_log, d_skip=self.d_skip, spread=SCAN_SPREAD)
+                        self.state, self.vdim, 0, dt_bias=self.dt_bias, a_log=self.a_log, d_skip=self.d_skip, spread=SCAN_SPREAD, work=work)
         normed = ctx.buf((n, inner), self.rt.dtype)
         ops.gated_group_norm(normed, y, u, 0, self.norm_w, self.norm_groups, self.eps, gate_first=True)
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)
@@ -134,7 +135,7 @@ class GatedLinearAttention(Part):
         return SlotState((self.heads * self.vdim * self.dim,), torch.float32)
 
     def scratch_row_bytes(self) -> int:
-        return 4 * (self.rows + self.qk + 2 * self.v) + 8 * self.hidden + 64
+        return 4 * (self.rows + 2 * self.qk + 2 * self.v) + 8 * self.hidden + 64
 
     def tensors(self):
         pre = self.prefix
@@ -166,8 +167,9 @@ class GatedLinearAttention(Part):
         z = ctx.buf((n, self.qk), f32)  # the decays' logits, one per key channel
         self.a2(z, low, buf=ctx.buf)
         y = ctx.buf((n, self.v), f32)
+        work = ctx.buf((ops.linear_scan_work(n, self.heads, self.dim, 1),), f32)
         ops.linear_scan(y, u, 2 * self.qk, u, self.qk, u, 0, z, 0, cache.state, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.heads, self.dim,
-                        self.vdim, 1, tau=self.tau, q_scale=self.dim ** -0.5, spread=SCAN_SPREAD)
+                        self.vdim, 1, tau=self.tau, q_scale=self.dim ** -0.5, spread=SCAN_SPREAD, work=work)
         normed = ctx.buf((n, self.v), self.rt.dtype)
         ops.gated_group_norm(normed, y, u, 2 * self.qk + self.v, self.norm_w, self.heads, self.eps, gate_first=False)
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)
