@@ -795,6 +795,7 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int slice_begin = blockIdx.z * args.k_slices_per_split;
   int n_slices = min(total_slices, slice_begin + args.k_slices_per_split) - slice_begin;
   int w_row = f0;       // the first weight row of this tile (by tile: inside the tile's batch)
+  int w_base = 0;       // by tile: the first row of the tile's batch in the stacked weight
   bool no_tile = false; // by tile: this token tile names no batch, nothing is computed or stored
 
   if (threadIdx.x == 0) {
@@ -817,8 +818,8 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int k = (slice_begin + i) * BK;
     mbar_expect_tx(&full_bar[s], STAGE_BYTES);
     if (GATED) {
-      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, f0);
-      tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, args.N + f0);
+      tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, w_base + f0);
+      tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, &full_bar[s], k, w_base + args.N + f0);
     } else {
       tma_load_2d(stage + A_BYTES, &map_w, &full_bar[s], k, w_row);
     }
@@ -842,7 +843,8 @@ gemm_tc_tokens_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       no_tile = true;
       n_slices = 0;
     } else {
-      w_row = batch * args.N + f0;
+      w_base = batch * (GATED ? 2 : 1) * args.N;  // a gated batch holds its gate rows, then its up rows
+      w_row = w_base + f0;
     }
   }
 
@@ -1618,8 +1620,8 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   epi &= 15;
   if (act && (epi != EPI_STORE || b_kind != B_ROWS)) return ALOFA_ERR_ARGUMENT;
   if (acc && (epi != EPI_RESIDUAL || bn <= 0)) return ALOFA_ERR_ARGUMENT;
-  // by tile: tokens on M, whole tiles of 128 rows, a stored product without bias or depth split
-  if (tile_batch && (bn >= 0 || epi != EPI_STORE || bias || splits > 1 || b_kind != B_ROWS || batches <= 0 || (T & 127))) return ALOFA_ERR_ARGUMENT;
+  // by tile: tokens on M, whole tiles of 128 rows, a stored or gated product without bias or depth split
+  if (tile_batch && (bn >= 0 || (epi != EPI_STORE && epi != EPI_GATED) || bias || splits > 1 || b_kind != B_ROWS || batches <= 0 || (T & 127))) return ALOFA_ERR_ARGUMENT;
   if (b_kind == B_NORMED) {
     if (bn != 16 || T > 16 || epi != EPI_GATED || !b_src || !n_gamma || !n_out || n_out == b_src || (K % 8) != 0 || !do_reduce) return ALOFA_ERR_ARGUMENT;
     if (((uintptr_t)b_src & 15) || ((uintptr_t)n_gamma & 15) || ((uintptr_t)n_out & 15) || ((uintptr_t)n_acc & 15) || ((uintptr_t)n_zero & 15)) return ALOFA_ERR_ARGUMENT;
@@ -1637,7 +1639,7 @@ ALOFA_API int alofa_gemm_tc(void* out, const void* x, const void* w, const float
   if (splits < 1) splits = 1;
   if (splits > total_slices) splits = total_slices;
   if (splits > 1 && !partial && !acc && b_kind != B_NORMED) return ALOFA_ERR_ARGUMENT;
-  const int w_rows = tile_batch ? batches * N : (epi == EPI_GATED) ? 2 * N : N;
+  const int w_rows = (tile_batch ? batches : 1) * ((epi == EPI_GATED) ? 2 * N : N);
   // bn > 0: weights on the M side, bn tokens per CTA.  bn < 0: tokens on the M
   // side (128 per CTA), -bn weight rows per MMA (for GATED half gate, half up).
   const bool tokens_on_m = bn < 0;

@@ -354,9 +354,11 @@ ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, co
   float* a_out = work;
   float* dt_out = mode ? nullptr : work + count;
   launch_dep(scan_decays_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, a_out, dt_out, dec, ldd, d_off, dt_bias, A_log, tau_inv, count, cols, mode);
-  // key channels a thread holds (4 * J): 16 measured best from 128 key channels on, for prompts (0.65 ms for 2,048 tokens of 32 heads
-  // of 128 x 64 against 0.67 with 8) and for decode steps (53 us for 64 requests against 86)
-  const int J = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 512 ? 4 : 8));
+  // Key channels a thread holds (4 * J), measured on 32 heads of 128 x 64: decode steps (64 requests, a token each) are fastest
+  // with 16 and 32 value channels a block (53 us against 67 with 8 and 16: fewer, longer loads of the state); prompts (2,048
+  // tokens of one request) with 8 and 16 value channels a block (0.62 ms against 0.71: more warps to hide each other's waits).
+  const bool prompt_like = n_tokens > 4 * n_seqs;
+  const int J = N <= 32 ? 1 : (N <= 64 ? 2 : (N <= 256 ? (prompt_like ? 2 : 4) : (N <= 512 ? 4 : 8)));
   const int R = 4 * J;
   int NS = 1;
   while (NS * R < N) NS *= 2;
@@ -365,7 +367,7 @@ ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, co
                    ((uintptr_t)v % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)c % 16 == 0) && ((uintptr_t)work % 16 == 0);
   int PC = 2 * (512 / NS);  // value channels per block: two a thread
   while (PC > 4 && PC / 2 >= P) PC /= 2;
-  if (PC > 32) PC = 32;  // more blocks of fewer warps: measured best at 32 value channels a block for prompts and decode steps alike
+  if (PC > (prompt_like ? 16 : 32)) PC = prompt_like ? 16 : 32;  // more blocks of fewer warps (see above)
   while (PC > 8 && (long long)H * n_seqs * ((P + PC - 1) / PC) < spread) PC /= 2;
   if (PC < 4) PC = 4;
   const int threads = ((PC / 2) * NS + 31) / 32 * 32;

@@ -373,8 +373,9 @@ def gemm_tc(out, x, w, bias, epi: int, bn: int, splits: int = 1, partial=None, s
     ``act`` (EPI_STORE only): a code of ``ACTIVATIONS`` applied to the fp32
     sums plus bias before they are stored.
 
-    ``tile_batch`` (int32 on the device; tokens on M, EPI_STORE, no bias):
-    ``w`` is [batches * N, K] and the i-th tile of 128 token rows multiplies
+    ``tile_batch`` (int32 on the device; tokens on M, EPI_STORE or EPI_GATED,
+    no bias): ``w`` is [batches * N, K] (gated: [batches * 2N, K], a batch's
+    gate rows before its up rows) and the i-th tile of 128 token rows multiplies
     by the rows of batch ``tile_batch[i]``; a negative entry skips the tile."""
     n = out.shape[1]
     rows_w = (2 * n if epi == EPI_GATED else n) * (batches if tile_batch is not None else 1)
@@ -733,6 +734,20 @@ def gemm_by_tile(out, x, w, tile_batch, tile_rows: int, act: str = "none") -> No
         if gemm_tc(out, x, w.view(batches * n, k), None, EPI_STORE, wide, act=ACTIVATIONS[act], tile_batch=tile_batch, batches=batches):
             return
     gemm_batched(out, x, w, 1, rows, n, k, k, 0, k, n * k, n, 0, act=act, tile_batch=tile_batch, tile_rows=tile_rows)
+
+
+def gemm_by_tile_gated(out, x, w, tile_batch, tile_rows: int) -> bool:
+    """``out[rows of tile i] = silu(x_i @ Wg^T) * (x_i @ Wu^T)`` with ``w``
+    [batches, 2N, K] holding each batch's gate rows before its up rows: the
+    tcgen05 product with the gated epilogue.  False, having launched nothing,
+    for operands it does not take (the caller then multiplies and gates in
+    two steps)."""
+    batches, n2, k = w.shape
+    rows = x.shape[0]
+    if (tile_rows != MOE_TILE_TC or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k % 8 or rows % 128 or n2 % 2
+            or os.environ.get("ALOFA_BY_TILE_TC", "1") == "0"):
+        return False
+    return gemm_tc(out, x, w.view(batches * n2, k), None, EPI_GATED, -256, tile_batch=tile_batch, batches=batches)
 
 
 def moe_route(choice, weight, gate, z, experts: int, top: int, softmax: bool = False, renormalize: bool = False) -> None:

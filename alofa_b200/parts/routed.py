@@ -118,9 +118,11 @@ class RoutedExperts(Part):
         ops.moe_scatter(xs, x, weight if self.weight_on_input else None, dest, top)
         mid = ctx.buf((rows, self.ff), dt)
         if self.gated:
-            both = ctx.buf((rows, 2 * self.ff), f32)
-            ops.gemm_by_tile(both, xs, self.up, tile_expert, tile)
-            ops.gate_up(mid, both)
+            # gate and up in one product whose epilogue multiplies them (the tcgen05 kernel), else the sums of both and a kernel that gates
+            if not ops.gemm_by_tile_gated(mid, xs, self.up, tile_expert, tile):
+                both = ctx.buf((rows, 2 * self.ff), f32)
+                ops.gemm_by_tile(both, xs, self.up, tile_expert, tile)
+                ops.gate_up(mid, both)
         else:
             ops.gemm_by_tile(mid, xs, self.up, tile_expert, tile, act=self.act)
         ys = ctx.buf((rows, self.hidden), f32)

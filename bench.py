@@ -546,7 +546,13 @@ class KernelClock:
             y, n_seqs, heads, groups, n, p = args[0], args[12], args[13], args[14], args[15], args[16]
             rows = y.shape[0]
             byts = 4 * rows * (2 * heads * p + 2 * groups * n + (heads * n if args[17] else heads)) + 8 * n_seqs * heads * n * p
-            flops = 0.0  # fp32 arithmetic, none of it on the tensor cores: the state's bytes are the bound
+            # the recurrence is 32-bit by the design: a multiply and two multiply-adds per state element and token on the fp32 pipe
+            # (no tensor-core mode is 32-bit), against the nominal fp32 rate: 128 lanes x 2 x 1.965 GHz per SM
+            import torch as _t
+
+            fp32_rate = _t.cuda.get_device_properties(0).multi_processor_count * 128 * 2 * 1.965e9
+            ideal = max(5.0 * rows * heads * n * p / fp32_rate, byts / (self.peaks["hbm_gbs"] * 1e9)) * 1e6
+            return ideal, 5.0 * rows * heads * n * p, byts
         elif name == "causal_conv":
             out = args[0]
             byts = 8 * out.numel() + 8 * args[9] * (args[3].shape[1] - 1) * out.shape[1]

@@ -324,6 +324,29 @@ def test_router_with_correction_and_identity_experts(experts, identity, top):
     assert_close(y.cpu(), want, 1e-5, "combined")
 
 
+@pytest.mark.parametrize("hidden,ff", [(64, 72), (128, 320), (192, 64)])
+def test_gated_products_by_tile_on_the_tcgen05_kernel(hidden, ff):
+    """Tiles of 128 sorted rows, each multiplied by its expert's gate and up rows with silu(gate) * up in the
+    epilogue; a tile that names no expert is left alone."""
+    from alofa_b200.csrc import ops
+
+    rng = np.random.default_rng(12)
+    experts, tiles = 3, 5
+    tile_expert = np.array([2, 0, -1, 1, 2], dtype=np.int32)
+    x = rounded(rng.standard_normal((tiles * 128, hidden)), BF16)
+    w = rounded(rng.standard_normal((experts, 2 * ff, hidden)) / np.sqrt(hidden), BF16)
+    out = torch.full((tiles * 128, ff), 3.0, dtype=BF16, device="cuda")
+    assert ops.gemm_by_tile_gated(out, dev(x, BF16), dev(w, BF16), dev(tile_expert), 128)
+    got = out.float().cpu().numpy()
+    for i, e in enumerate(tile_expert):
+        rows = slice(i * 128, (i + 1) * 128)
+        if e < 0:
+            assert (got[rows] == 3.0).all()
+            continue
+        want = plain.silu(x[rows] @ w[e, :ff].T) * (x[rows] @ w[e, ff:].T)
+        assert_close(got[rows], want, KERNEL_TOL[BF16], f"tile {i}")
+
+
 # ---------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------
