@@ -56,6 +56,8 @@ class StateSpaceMixer(Part):
         self.taps, self.norm_groups, self.eps = int(p("conv")), int(p("norm_groups")), float(p("eps"))
         if min(self.heads, self.vdim, self.state, self.groups, self.taps, self.norm_groups) <= 0 or self.heads % self.groups:
             raise AlofaError("invalid_argument", "state-space sizes must be positive and groups must divide heads", f"params={self.params}")
+        if self.state > 1024:
+            raise AlofaError("unsupported", "the recurrence kernel holds at most 1,024 key channels a head", f"state={self.state}")
         self.inner = self.heads * self.vdim
         if self.inner % self.norm_groups:
             raise AlofaError("invalid_argument", "norm_groups must divide heads * vdim", f"inner={self.inner} norm_groups={self.norm_groups}")
@@ -127,6 +129,8 @@ class GatedLinearAttention(Part):
         self.tau, self.eps = float(p("tau")), float(p("eps"))
         if min(self.heads, self.dim, self.vdim) <= 0 or self.tau <= 0:
             raise AlofaError("invalid_argument", "gated linear attention sizes and tau must be positive", f"params={self.params}")
+        if self.dim > 1024:
+            raise AlofaError("unsupported", "the recurrence kernel holds at most 1,024 key channels a head", f"dim={self.dim}")
         self.qk, self.v = self.heads * self.dim, self.heads * self.vdim
         self.rows = 2 * self.qk + 2 * self.v  # [q | k | v | g]
         self.rank = None  # the decay's inner size, from the tensor's shape
