@@ -29,7 +29,7 @@ pytestmark = pytest.mark.gpu
 F32, BF16 = torch.float32, torch.bfloat16
 TOL = {"float32": 2e-5, "bfloat16": 9e-2}
 KERNEL_TOL = {F32: 1e-5, BF16: 2e-2}
-LENGTHS = {"A": [1, 2, 37, 64, 65, 130], "B": [3, 16, 17, 33, 80], "C": [5, 63, 129, 200]}
+LENGTHS = {"A": [1, 2, 37, 64, 65, 130], "B": [3, 16, 17, 33, 80], "C": [5, 63, 129, 200], "D": [2, 64, 150, 300]}
 DECODED = 12
 
 

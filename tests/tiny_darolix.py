@@ -51,6 +51,11 @@ CONFIGS = {
     "C": {"architecture": "Darolix", "vocab": 320, "width": 128, "norm": {"eps": 1e-6}, "embedding": {"scale": 11.3}, "loop": {"start": 0, "stop": 1, "times": 3},
           "layers": [layer("parallel", pair(4, 2, 64, 64, 0.125, 20.0, (0.3, 16), 2, 64, 64, 16.0), moe(4, 1, 2, 64)),
                      layer("mamba2", mamba(4, 64, 64, 2, 4, 2), moe(4, 1, 2, 64))]},
+    # head sizes of 128 and of 32 for keys and values alike (the tensor-core attention kernels, capped and not), pages of 64
+    "D": {"architecture": "Darolix", "vocab": 190, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+          "layers": [layer("parallel", pair(2, 1, 128, 128, 0.09, 8.0, (0.4, 32), 1, 32, 16, 3.0), moe(3, 1, 2, 32)),
+                     layer("parallel", pair(4, 4, 32, 32, 0.2, 0.0, None, 2, 16, 32, 8.0), None),
+                     layer("mamba2", mamba(2, 16, 8, 1, 4, 1), moe(3, 1, 2, 32))]},
 }
 
 
