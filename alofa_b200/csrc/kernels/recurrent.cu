@@ -125,8 +125,7 @@ ALOFA_API int alofa_causal_conv(float* out, const float* u, int ld, int offset, 
 // ---------------------------------------------------------------------------
 // The recurrence, in two kernels.
 //
-// scan_decays: what the recurrence multiplies by (or, for the chunked form below, its logarithm), once per token, in fp32 with the
-// precise library functions:
+// scan_decays: what the recurrence multiplies by, once per token, in fp32 with the precise library functions:
 //   mode 0 (one decay per head and token): dt = softplus(dec[t, h] + dt_bias[h]) and a = exp(-exp(A_log[h]) * dt)
 //   mode 1 (one decay per key channel):    a[n] = exp(log_sigmoid(dec[t, h, n]) / tau) = sigmoid(.)^(1/tau)
 //
@@ -143,7 +142,7 @@ ALOFA_API int alofa_causal_conv(float* out, const float* u, int ld, int offset, 
 //   mode 1: k_t = b[t, h, :],        q_t = c[t, h, :] * q_scale
 // ---------------------------------------------------------------------------
 __global__ void scan_decays_kernel(float* __restrict__ a_out, float* __restrict__ dt_out, const float* __restrict__ dec, int ldd, int d_off,
-                                   const float* __restrict__ dt_bias, const float* __restrict__ A_log, float tau_inv, long long count, int cols, int mode, int logs) {
+                                   const float* __restrict__ dt_bias, const float* __restrict__ A_log, float tau_inv, long long count, int cols, int mode) {
   pdl_begin();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= count) return;
@@ -153,9 +152,9 @@ __global__ void scan_decays_kernel(float* __restrict__ a_out, float* __restrict_
   if (mode == 0) {
     const float dt = softplus_f(z + (dt_bias ? dt_bias[c] : 0.f));
     dt_out[i] = dt;
-    a_out[i] = logs ? -expf(A_log[c]) * dt : expf(-expf(A_log[c]) * dt);
+    a_out[i] = expf(-expf(A_log[c]) * dt);
   } else {
-    a_out[i] = logs ? -softplus_f(-z) * tau_inv : expf(-softplus_f(-z) * tau_inv);
+    a_out[i] = expf(-softplus_f(-z) * tau_inv);
   }
 }
 
@@ -341,262 +340,20 @@ static int linear_scan_launch(const ScanArgs& a, int n_seqs, int threads, size_t
   return launch_status();
 }
 
-// ---------------------------------------------------------------------------
-// The same recurrence for long portions of prompts, taken 16 tokens at a time.  With L_t the running sum
-// of the logarithms of the decays inside a chunk (per key channel, or one for all), S0 the state at the
-// chunk's start and C its last token,
-//
-//   y_t = (q_t . exp(L_t))^T S0 + sum_{s <= t} M[t][s] v_s,   M[t][s] = sum_n q_t[n] k_s[n] exp(L_t[n] - L_s[n])
-//   S_C = exp(L_C) . S0 + sum_s (k_s . exp(L_C - L_s)) v_s^T
-//
-// Every exponent is a difference of running sums that is never positive, so nothing overflows however
-// strong the decays.  scan_chunk_prepare makes q . exp(L_t), k . exp(L_C - L_s), exp(L_C) and M for every
-// chunk of every request and head at once (nothing in them depends on the state); scan_chunk_apply then
-// walks a request's chunks in order with the state of one head and 32 value channels in shared memory:
-// per chunk three small fp32 products whose operands come in by asynchronous copies, the next chunk's
-// while this one is worked on.  All fp32 multiply-adds; for every output the order of additions is fixed
-// by the sizes and by where the portion starts.
-// ---------------------------------------------------------------------------
-constexpr int CH = 16;        // tokens a chunk
-constexpr int CH_PC = 32;     // value channels a block of scan_chunk_apply
-constexpr int CH_PCP = 33;    // a state row in shared memory, padded
-
-// slot = request * max_chunks + chunk.  QH, KH [slot][H][N][CH] (token fastest), AB [slot][H][N], MM [slot][H][CH][CH].
-template <int MODE>
-__global__ void __launch_bounds__(128) scan_chunk_prepare_kernel(float* __restrict__ QH, float* __restrict__ KH, float* __restrict__ AB, float* __restrict__ MM,
-                                                                 const float* __restrict__ k, int ldk, int k_off, const float* __restrict__ q, int ldq,
-                                                                 int q_off, const float* __restrict__ la, const float* __restrict__ dt,
-                                                                 const int* __restrict__ q_start, int H, int G, int N, int max_chunks, float q_scale) {
-  __shared__ float partial[4][CH * CH];
-  pdl_begin();
-  const int chunk = blockIdx.x, s = blockIdx.y, h = blockIdx.z;
-  const int t0 = q_start[s], t1 = q_start[s + 1];
-  const int c0 = t0 + chunk * CH;
-  if (c0 >= t1) return;
-  const int live = min(CH, t1 - c0);
-  const int g = h / (H / G);
-  const size_t slot = (size_t)s * max_chunks + chunk;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float m[CH * (CH + 1) / 2];
-#pragma unroll
-  for (int i = 0; i < CH * (CH + 1) / 2; ++i) m[i] = 0.f;
-  for (int n = threadIdx.x; n < N; n += 128) {
-    float L[CH], qv[CH], kv[CH];
-    float run = 0.f;
-#pragma unroll
-    for (int t = 0; t < CH; ++t) {
-      if (t < live) {
-        const size_t row = c0 + t;
-        run += MODE ? la[row * ((size_t)H * N) + h * N + n] : la[row * H + h];
-        qv[t] = q[row * ldq + q_off + g * N + n] * q_scale;
-        kv[t] = k[row * ldk + k_off + g * N + n] * (MODE ? 1.f : dt[row * H + h]);
-      } else {
-        qv[t] = kv[t] = 0.f;
-      }
-      L[t] = run;
-    }
-    float* qh = QH + ((slot * H + h) * N + n) * CH;
-    float* kh = KH + ((slot * H + h) * N + n) * CH;
-#pragma unroll
-    for (int t = 0; t < CH; t += 4) {
-      *reinterpret_cast<float4*>(qh + t) = make_float4(qv[t] * expf(L[t]), qv[t + 1] * expf(L[t + 1]), qv[t + 2] * expf(L[t + 2]), qv[t + 3] * expf(L[t + 3]));
-      *reinterpret_cast<float4*>(kh + t) = make_float4(kv[t] * expf(run - L[t]), kv[t + 1] * expf(run - L[t + 1]), kv[t + 2] * expf(run - L[t + 2]),
-                                                        kv[t + 3] * expf(run - L[t + 3]));
-    }
-    AB[(slot * H + h) * N + n] = expf(run);
-    int at = 0;
-#pragma unroll
-    for (int t = 0; t < CH; ++t)
-#pragma unroll
-      for (int u = 0; u <= t; ++u) m[at++] += qv[t] * kv[u] * expf(L[t] - L[u]);
-  }
-  // the key channels' shares of M: over the lanes in butterfly order, then over the warps in their order
-  {
-    int at = 0;
-#pragma unroll
-    for (int t = 0; t < CH; ++t)
-#pragma unroll
-      for (int u = 0; u <= t; ++u) {
-        const float v = warp_sum(m[at++]);
-        if (lane == 0) partial[warp][t * CH + u] = v;
-      }
-  }
-  __syncthreads();
-  float* mm = MM + (slot * H + h) * CH * CH;
-  for (int e = threadIdx.x; e < CH * CH; e += 128) {
-    const int t = e / CH, u = e - t * CH;
-    mm[e] = u <= t ? ((partial[0][e] + partial[1][e]) + partial[2][e]) + partial[3][e] : 0.f;
-  }
-}
-
-struct ChunkArgs {
-  float* y; const float* v; int ldv, v_off;
-  const float* QH; const float* KH; const float* AB; const float* MM;
-  const float* D; float* state; long long slot_stride;
-  const int* q_start; const int* state_slots;
-  int H, N, P, max_chunks;
-};
-
-__global__ void __launch_bounds__(128) scan_chunk_apply_kernel(const ChunkArgs a) {
-  extern __shared__ __align__(16) float ch_smem[];
-  const int N = a.N, P = a.P, H = a.H;
-  const int NP = (N + 3) & ~3;
-  float* S = ch_smem;                       // [N][CH_PCP]
-  float* stage0 = S + (size_t)NP * CH_PCP + 3;
-  stage0 = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(stage0) + 15) & ~(uintptr_t)15);
-  const int per_stage = 2 * NP * CH + CH * CH_PC + CH * CH + NP;  // QT, KT [N][CH]; V [CH][PC]; M [CH][CH]; AB [N]
-  const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * CH_PC;
-  const int tid = threadIdx.x;
-  const int grp = tid >> 5, p = tid & 31;
-  const bool p_ok = p0 + p < P;
-  for (int e = tid; e < 2 * per_stage; e += 128) stage0[e] = 0.f;  // value channels past P stay zero
-  pdl_begin();
-  const int t0 = a.q_start[s], t1 = a.q_start[s + 1];
-  float* G = a.state + (long long)a.state_slots[s] * a.slot_stride + (size_t)h * P * N;  // [p][n]
-  for (int e = tid; e < CH_PC * N; e += 128) {
-    const int pp = e / N, n = e - pp * N;
-    S[n * CH_PCP + pp] = p0 + pp < P ? G[(size_t)(p0 + pp) * N + n] : 0.f;
-  }
-  const float dskip = a.D ? a.D[h] : 0.f;
-  __syncthreads();
-
-  auto fetch = [&](int which, int chunk) {
-    float* QT = stage0 + which * per_stage;
-    float* KT = QT + NP * CH;
-    float* V = KT + NP * CH;
-    float* M = V + CH * CH_PC;
-    float* AB = M + CH * CH;
-    const size_t slot = (size_t)s * a.max_chunks + chunk;
-    const float* qh = a.QH + (slot * H + h) * N * CH;
-    const float* kh = a.KH + (slot * H + h) * N * CH;
-    for (int e = tid; e < N * CH / 4; e += 128) {
-      cp_async_16(QT + e * 4, qh + e * 4);
-      cp_async_16(KT + e * 4, kh + e * 4);
-    }
-    const float* mm = a.MM + (slot * H + h) * CH * CH;
-    for (int e = tid; e < CH * CH / 4; e += 128) cp_async_16(M + e * 4, mm + e * 4);
-    const float* ab = a.AB + (slot * H + h) * N;
-    for (int e = tid; e < N; e += 128) cp_async_4(AB + e, ab + e);
-    const int c0 = t0 + chunk * CH, live = min(CH, t1 - c0);
-    for (int e = tid; e < live * CH_PC; e += 128) {
-      const int tt = e / CH_PC, c = e - tt * CH_PC;
-      if (p0 + c < P) cp_async_4(V + tt * CH_PC + c, a.v + (size_t)(c0 + tt) * a.ldv + a.v_off + h * P + p0 + c);
-    }
-  };
-
-  const int chunks = (t1 - t0 + CH - 1) / CH;
-  if (chunks > 0) fetch(0, 0);
-  for (int chunk = 0; chunk < chunks; ++chunk) {
-    const int which = chunk & 1;
-    cp_async_done();
-    __syncthreads();  // this chunk's operands are here, the state is up to date, the other stage is free
-    if (chunk + 1 < chunks) fetch(which ^ 1, chunk + 1);
-    const float* QT = stage0 + which * per_stage;
-    const float* KT = QT + NP * CH;
-    const float* V = KT + NP * CH;
-    const float* M = V + CH * CH_PC;
-    const float* AB = M + CH * CH;
-    const int c0 = t0 + chunk * CH, live = min(CH, t1 - c0);
-    // outputs: this thread's value channel, tokens 4 * grp .. 4 * grp + 3
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int n = 0; n < N; ++n) {
-      const float sv = S[n * CH_PCP + p];
-      const float4 q4 = *reinterpret_cast<const float4*>(QT + n * CH + 4 * grp);
-      acc[0] = fmaf(q4.x, sv, acc[0]);
-      acc[1] = fmaf(q4.y, sv, acc[1]);
-      acc[2] = fmaf(q4.z, sv, acc[2]);
-      acc[3] = fmaf(q4.w, sv, acc[3]);
-    }
-    float vreg[CH];
-#pragma unroll
-    for (int u = 0; u < CH; ++u) vreg[u] = u < live ? V[u * CH_PC + p] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int t = 4 * grp + i;
-#pragma unroll
-      for (int u = 0; u < CH; ++u) acc[i] = fmaf(M[t * CH + u], vreg[u], acc[i]);  // zero above the diagonal
-      if (t < live && p_ok) a.y[(size_t)(c0 + t) * H * P + h * P + p0 + p] = acc[i] + dskip * V[t * CH_PC + p];
-    }
-    __syncthreads();  // every output has read the old state
-    // the state moves on: this thread's value channel, a quarter of the key channels
-    const int quarter = (N + 3) / 4;
-    for (int n = grp * quarter; n < min(N, (grp + 1) * quarter); ++n) {
-      float sum = AB[n] * S[n * CH_PCP + p];
-      const float4* k4 = reinterpret_cast<const float4*>(KT + n * CH);
-#pragma unroll
-      for (int j = 0; j < CH / 4; ++j) {
-        const float4 kk = k4[j];
-        sum = fmaf(kk.x, vreg[4 * j], sum);
-        sum = fmaf(kk.y, vreg[4 * j + 1], sum);
-        sum = fmaf(kk.z, vreg[4 * j + 2], sum);
-        sum = fmaf(kk.w, vreg[4 * j + 3], sum);
-      }
-      S[n * CH_PCP + p] = sum;
-    }
-  }
-  __syncthreads();
-  for (int e = tid; e < CH_PC * N; e += 128) {
-    const int pp = e / N, n = e - pp * N;
-    if (p0 + pp < P) G[(size_t)(p0 + pp) * N + n] = S[n * CH_PCP + pp];
-  }
-}
-
-static size_t scan_chunk_smem(int N) {
-  const int NP = (N + 3) & ~3;
-  return ((size_t)NP * CH_PCP + 8 + 2 * (size_t)(2 * NP * CH + CH * CH_PC + CH * CH + NP)) * sizeof(float);
-}
-
-// How many fp32 numbers of scratch the chunked form needs beside the decays' (0: it does not take these sizes).
-ALOFA_API long long alofa_linear_scan_chunk_work(int n_seqs, int max_q_len, int H, int N) {
-  if (N > 256 || N % 4) return 0;
-  const long long slots = (long long)n_seqs * ((max_q_len + CH - 1) / CH);
-  return slots * H * ((long long)2 * N * CH + N + CH * CH);
-}
-
 // work: fp32 scratch of n_tokens * (mode 0: 2 * H; mode 1: H * N) numbers for the decays.  spread: how many blocks the scan
 // should have at least, if the value channels allow it (a prompt of one request has few (request, head) pairs; its value
 // channels are dealt to more blocks).
 ALOFA_API int alofa_linear_scan(float* y, const float* v, int ldv, int v_off, const float* b, int ldb, int b_off, const float* c, int ldc, int c_off,
                                 const float* dec, int ldd, int d_off, const float* dt_bias, const float* A_log, const float* D, float tau_inv, float q_scale,
                                 float* state, long long slot_stride, const int* q_start, const int* state_slots, int n_tokens, int n_seqs, int H, int G, int N,
-                                int P, int mode, int spread, float* work, int chunk_q_len, float* chunk_work, cudaStream_t stream) {
+                                int P, int mode, int spread, float* work, cudaStream_t stream) {
   if (n_seqs <= 0 || n_tokens <= 0) return ALOFA_OK;
   if (H <= 0 || G <= 0 || H % G || N <= 0 || N > 1024 || P <= 0 || !work || (mode == 0 && !A_log)) return ALOFA_ERR_ARGUMENT;
   const int cols = mode ? H * N : H;
   const long long count = (long long)n_tokens * cols;
   float* a_out = work;
   float* dt_out = mode ? nullptr : work + count;
-  // chunk_q_len > 0 with chunk_work: the chunked form; chunk_q_len is the most tokens a request has in this step (it sizes the
-  // chunks' scratch, [request][chunk])
-  const bool chunked = chunk_work && chunk_q_len > 0 && alofa_linear_scan_chunk_work(n_seqs, chunk_q_len, H, N) > 0 && scan_chunk_smem(N) <= 200 * 1024;
-  launch_dep(scan_decays_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, a_out, dt_out, dec, ldd, d_off, dt_bias, A_log, tau_inv, count, cols, mode,
-             chunked ? 1 : 0);
-  if (chunked) {
-    const int max_chunks = (chunk_q_len + CH - 1) / CH;
-    const long long slots = (long long)n_seqs * max_chunks;
-    float* QH = chunk_work;
-    float* KH = QH + slots * H * N * CH;
-    float* AB = KH + slots * H * N * CH;
-    float* MM = AB + slots * H * N;
-    if (((uintptr_t)chunk_work & 15) || max_chunks > 65535 || H > 65535 || n_seqs > 65535) return ALOFA_ERR_ARGUMENT;
-    const dim3 pgrid(max_chunks, n_seqs, H);
-    if (mode)
-      launch_dep(scan_chunk_prepare_kernel<1>, pgrid, 128, 0, stream, QH, KH, AB, MM, b, ldb, b_off, c, ldc, c_off, (const float*)a_out, (const float*)dt_out, q_start, H, G,
-                 N, max_chunks, q_scale);
-    else
-      launch_dep(scan_chunk_prepare_kernel<0>, pgrid, 128, 0, stream, QH, KH, AB, MM, b, ldb, b_off, c, ldc, c_off, (const float*)a_out, (const float*)dt_out, q_start, H, G,
-                 N, max_chunks, q_scale);
-    const size_t smem = scan_chunk_smem(N);
-    static size_t set = 48 * 1024;
-    if (smem > set) {
-      if (cudaFuncSetAttribute(scan_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return ALOFA_ERR_LAUNCH;
-      set = smem;
-    }
-    ChunkArgs ca = {y, v, ldv, v_off, QH, KH, AB, MM, mode ? nullptr : D, state, slot_stride, q_start, state_slots, H, N, P, max_chunks};
-    launch_dep(scan_chunk_apply_kernel, dim3(H, n_seqs, (P + CH_PC - 1) / CH_PC), 128, smem, stream, ca);
-    return launch_status();
-  }
+  launch_dep(scan_decays_kernel, (unsigned)((count + 255) / 256), 256, 0, stream, a_out, dt_out, dec, ldd, d_off, dt_bias, A_log, tau_inv, count, cols, mode);
   // Key channels a thread holds (4 * J), measured on 32 heads of 128 x 64: decode steps (64 requests, a token each) are fastest
   // with 16 and 32 value channels a block (53 us against 67 with 8 and 16: fewer, longer loads of the state); prompts (2,048
   // tokens of one request) with 8 and 16 value channels a block (0.62 ms against 0.71: more warps to hide each other's waits).

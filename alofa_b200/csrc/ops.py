@@ -877,15 +877,14 @@ def _recurrent():
             "alofa_embed_scaled": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
             "alofa_add_rows": [_P, _P, _L, _P],
             "alofa_causal_conv": [_P, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _P],
-            "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P],
-            "alofa_linear_scan_chunk_work": [_I, _I, _I, _I],
+            "alofa_linear_scan": [_P, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _I, _I, _P, _P, _P, _F, _F, _P, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
             "alofa_gated_group_norm": [_P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _F, _I, _I, _P],
             "alofa_branch_norm_add": [_P, _P, _P, _P, _P, _I, _I, _F, _F, _P],
             "alofa_qkv_prepare": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I, _P],
         }
         for name, args in sigs.items():
             fn = getattr(lib, name)
-            fn.restype = _L if name == "alofa_linear_scan_chunk_work" else _I
+            fn.restype = _I
             fn.argtypes = args
         _libs["recurrent"] = lib
     return lib
@@ -942,8 +941,7 @@ def causal_conv(out, u, offset: int, w, bias, state, q_start, state_slots, seq_o
 
 
 def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int, state, q_start, state_slots, n_seqs: int, heads: int, groups: int, n: int, p: int,
-                mode: int, dt_bias=None, a_log=None, d_skip=None, tau: float = 1.0, q_scale: float = 1.0, spread: int = 0, work=None, chunk_q_len: int = 0,
-                chunk_work=None) -> None:
+                mode: int, dt_bias=None, a_log=None, d_skip=None, tau: float = 1.0, q_scale: float = 1.0, spread: int = 0, work=None) -> None:
     """The recurrence ``S_t = diag(a_t) S_(t-1) + k_t v_t^T, y_t = S_t^T q_t``
     per head over each request's tokens of the step in order, all fp32; the
     state [slots, >= heads * p * n] (per head [p][n]) is read and left up to
@@ -954,12 +952,7 @@ def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int,
     queries shared by the heads of a group.  ``mode`` 1: one decay per key
     channel, ``a = sigmoid(dec[t, h, :]) ** (1 / tau)``, queries times
     ``q_scale``.  ``work``: fp32 scratch for the decays, :func:`linear_scan_work`
-    numbers (allocated when absent: callers inside a step pass step scratch).
-    ``chunk_q_len`` > 0 (the most tokens a request has in the step) with
-    ``chunk_work`` (:func:`linear_scan_chunk_work` numbers, not 0) takes the
-    chunked form for long portions of prompts: 16 tokens at a time as small
-    fp32 products, the same result up to the rounding of sums in another
-    order."""
+    numbers (allocated when absent: callers inside a step pass step scratch)."""
     f32, i32 = torch.float32, torch.int32
     rows = y.shape[0]
     if tuple(y.shape) != (rows, heads * p) or state.stride(0) < heads * p * n or state.dtype != f32 or not state.is_cuda:
@@ -974,18 +967,11 @@ def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int,
     if work.numel() < need:
         raise AlofaError("invalid_argument", "linear_scan scratch is too small", f"have={work.numel()} need={need}")
     count_launches(1)  # the kernel that makes the decays
-    if chunk_work is not None and chunk_q_len > 0:
-        if chunk_work.numel() < linear_scan_chunk_work(n_seqs, chunk_q_len, heads, n):
-            raise AlofaError("invalid_argument", "linear_scan chunk scratch is too small", f"have={chunk_work.numel()}")
-        count_launches(1)  # the kernel that prepares the chunks
-    else:
-        chunk_q_len, chunk_work = 0, None
     _done(
         _recurrent().alofa_linear_scan(
             _dev(y, "y", f32), _dev(v, "v"), v.shape[1], v_off, _dev(b, "b"), b.shape[1], b_off, _dev(c, "c"), c.shape[1], c_off, _dev(dec, "dec"), dec.shape[1], d_off,
             opt(dt_bias, "dt_bias"), opt(a_log, "a_log"), opt(d_skip, "d_skip"), 1.0 / float(tau), float(q_scale), state.data_ptr(), state.stride(0),
-            _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), rows, n_seqs, heads, groups, n, p, mode, spread, _dev(work, "work", f32),
-            int(chunk_q_len), _dev(chunk_work, "chunk_work", f32) if chunk_work is not None else None, _stream(),
+            _dev(q_start, "q_start", i32), _dev(state_slots, "state_slots", i32), rows, n_seqs, heads, groups, n, p, mode, spread, _dev(work, "work", f32), _stream(),
         ),
         "linear_scan", f"heads={heads} groups={groups} n={n} p={p} mode={mode}",
     )
@@ -994,12 +980,6 @@ def linear_scan(y, v, v_off: int, b, b_off: int, c, c_off: int, dec, d_off: int,
 def linear_scan_work(rows: int, heads: int, n: int, mode: int) -> int:
     """How many fp32 numbers of scratch :func:`linear_scan` needs."""
     return rows * (heads * n if mode else 2 * heads)
-
-
-def linear_scan_chunk_work(n_seqs: int, max_q_len: int, heads: int, n: int) -> int:
-    """How many fp32 numbers of scratch the chunked form of :func:`linear_scan`
-    needs; 0 when it does not take these sizes."""
-    return int(_recurrent().alofa_linear_scan_chunk_work(n_seqs, max_q_len, heads, n))
 
 
 def gated_group_norm(out, y, gate, g_off: int, w, groups: int, eps: float, gate_first: bool) -> None:

@@ -36,24 +36,6 @@ from .linear import RESIDUAL, STORE, Linear, add_into_stream
 SCAN_SPREAD = 128
 
 
-# Steps in which some request has this many tokens or more take the recurrence chunk by chunk (16 tokens at a time as small
-# fp32 products); shorter portions and decode steps walk the tokens one by one.  ALOFA_SCAN_CHUNKED=0 keeps the walk.
-CHUNKED_FROM = 64
-CHUNK_SCRATCH_LIMIT = 1 << 29  # fp32 numbers (2 GiB): beyond it the walk
-
-
-def _chunk_scratch(ctx, heads: int, n: int):
-    """(chunk_q_len, scratch) for the chunked form in this step, or (0, None)."""
-    import os
-
-    if ctx.max_q_len < CHUNKED_FROM or os.environ.get("ALOFA_SCAN_CHUNKED", "1") == "0":
-        return 0, None
-    need = ops.linear_scan_chunk_work(ctx.n_seqs, ctx.max_q_len, heads, n)
-    if need <= 0 or need > CHUNK_SCRATCH_LIMIT:
-        return 0, None
-    return ctx.max_q_len, ctx.buf((need,), torch.float32)
-
-
 def _project_out(ctx, linear_add: Linear, linear_store: Linear, h, x, store: bool) -> None:
     if store:
         linear_store(h, x, buf=ctx.buf)
@@ -127,10 +109,8 @@ class StateSpaceMixer(Part):
         ops.causal_conv(xbc, u, inner, self.conv_w, self.conv_b, st[:, self.scan_words:], ctx.q_start, ctx.state_slots, ctx.seq_of_token, ctx.n_seqs)
         y = ctx.buf((n, inner), f32)
         work = ctx.buf((ops.linear_scan_work(n, self.heads, self.state, 0),), f32)
-        chunk_q_len, chunk_work = _chunk_scratch(ctx, self.heads, self.state)
         ops.linear_scan(y, xbc, 0, xbc, inner, xbc, inner + bc, u, 2 * inner + 2 * bc, st, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.groups,
-                        self.state, self.vdim, 0, dt_bias=self.dt_bias, a_log=self.a_log, d_skip=self.d_skip, spread=SCAN_SPREAD, work=work,
-                        chunk_q_len=chunk_q_len, chunk_work=chunk_work)
+                        self.state, self.vdim, 0, dt_bias=self.dt_bias, a_log=self.a_log, d_skip=self.d_skip, spread=SCAN_SPREAD, work=work)
         normed = ctx.buf((n, inner), self.rt.dtype)
         ops.gated_group_norm(normed, y, u, 0, self.norm_w, self.norm_groups, self.eps, gate_first=True)
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)
@@ -192,10 +172,8 @@ class GatedLinearAttention(Part):
         self.a2(z, low, buf=ctx.buf)
         y = ctx.buf((n, self.v), f32)
         work = ctx.buf((ops.linear_scan_work(n, self.heads, self.dim, 1),), f32)
-        chunk_q_len, chunk_work = _chunk_scratch(ctx, self.heads, self.dim)
         ops.linear_scan(y, u, 2 * self.qk, u, self.qk, u, 0, z, 0, cache.state, ctx.q_start, ctx.state_slots, ctx.n_seqs, self.heads, self.heads, self.dim,
-                        self.vdim, 1, tau=self.tau, q_scale=self.dim ** -0.5, spread=SCAN_SPREAD, work=work,
-                        chunk_q_len=chunk_q_len, chunk_work=chunk_work)
+                        self.vdim, 1, tau=self.tau, q_scale=self.dim ** -0.5, spread=SCAN_SPREAD, work=work)
         normed = ctx.buf((n, self.v), self.rt.dtype)
         ops.gated_group_norm(normed, y, u, 2 * self.qk + self.v, self.norm_w, self.heads, self.eps, gate_first=False)
         _project_out(ctx, self.out_add, self.out_store, h, normed, store)

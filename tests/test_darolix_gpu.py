@@ -95,7 +95,7 @@ def test_short_convolution_carries_its_last_inputs(channels, taps):
     assert (state[[0, 2]] == 0).all() and (state[:, :3] == 0).all(), "state of another slot, or words before the convolution's, were written"
 
 
-def run_scan(mode, lengths, cuts, H, G, N, P, tau=1.0, seed=3, boost=None, chunked=False):
+def run_scan(mode, lengths, cuts, H, G, N, P, tau=1.0, seed=3, boost=None):
     """The recurrence over requests cut into portions, against the plain whole-sequence form."""
     from alofa_b200.csrc import ops
 
@@ -129,15 +129,10 @@ def run_scan(mode, lengths, cuts, H, G, N, P, tau=1.0, seed=3, boost=None, chunk
         v, b, c, dec = cat(0), cat(1), cat(2), cat(3)
         q_start, slots, _ = meta(counts, [slots_of[r] for r in live])
         y = torch.empty((v.shape[0], H * P), dtype=F32, device="cuda")
-        extra = {}
-        if chunked:  # 16 tokens at a time as small products, whatever the portions' lengths
-            need = ops.linear_scan_chunk_work(len(live), max(counts), H, N)
-            assert need > 0
-            extra = {"chunk_q_len": max(counts), "chunk_work": torch.empty((need,), dtype=F32, device="cuda")}
         if mode == 0:
-            ops.linear_scan(y, v, 0, b, 0, c, 0, dec, 0, state, q_start, slots, len(live), H, G, N, P, 0, dt_bias=dev(dt_bias, F32), a_log=dev(a_log, F32), d_skip=dev(d_skip, F32), **extra)
+            ops.linear_scan(y, v, 0, b, 0, c, 0, dec, 0, state, q_start, slots, len(live), H, G, N, P, 0, dt_bias=dev(dt_bias, F32), a_log=dev(a_log, F32), d_skip=dev(d_skip, F32))
         else:
-            ops.linear_scan(y, v, 0, b, 0, c, 0, dec, 0, state, q_start, slots, len(live), H, G, N, P, 1, tau=tau, q_scale=N ** -0.5, **extra)
+            ops.linear_scan(y, v, 0, b, 0, c, 0, dec, 0, state, q_start, slots, len(live), H, G, N, P, 1, tau=tau, q_scale=N ** -0.5)
         o = y.cpu().numpy()
         k = 0
         for r, cnt in zip(live, counts):
@@ -158,15 +153,6 @@ def test_recurrence_with_one_decay_per_head(H, G, N, P):
 @pytest.mark.parametrize("H,N,P,tau", [(3, 16, 40, 4.0), (2, 8, 8, 9.0), (5, 20, 4, 1.0), (2, 64, 64, 16.0), (1, 520, 3, 2.0)])
 def test_recurrence_with_one_decay_per_key_channel(H, N, P, tau):
     run_scan(1, [70, 33, 1], [2, 1, 17, 1, 40], H, H, N, P, tau=tau)
-
-
-@pytest.mark.parametrize("mode,H,G,N,P,tau", [(0, 5, 1, 16, 24, 1.0), (0, 6, 3, 24, 12, 1.0), (0, 2, 1, 128, 64, 1.0), (0, 3, 3, 4, 5, 1.0), (1, 3, 3, 16, 40, 4.0), (1, 2, 2, 64, 64, 16.0),
-                                                  (1, 2, 2, 8, 33, 0.05), (1, 1, 1, 256, 7, 2.0)])
-def test_recurrence_chunk_by_chunk(mode, H, G, N, P, tau):
-    """The chunked form (16 tokens at a time, chunks prepared for all requests at once) against the plain recurrence:
-    portions of 1, 2, 17, 40 and 100 tokens that start anywhere, requests that sit steps out, value channels that
-    do not fill a block, and decays so strong (tau 0.05) that ratios taken the wrong way round would overflow."""
-    run_scan(mode, [230, 33, 1], [1, 100, 17, 2, 40], H, G, N, P, tau=tau, chunked=True)
 
 
 def test_recurrence_keeps_a_far_token_and_a_freed_slot_starts_anew():
